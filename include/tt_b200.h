@@ -1,0 +1,138 @@
+/* Additive entry points of the B200 tinytorch library.
+ *
+ * Nothing here is needed by a program written against the reference headers;
+ * tensor.h and autograd.h alone are the drop-in surface.  These calls expose
+ * what the reference keeps in its Python gate scripts or does not have at
+ * all: device control, the backward kernels as stand-alone operators (so
+ * that each can be checked and timed on its own), a fused loss, on-device
+ * optimiser steps, persistent parameters, and data-parallel gradient
+ * reduction over NCCL.  Each comment names the reference code the call
+ * stands in for (file:line inside the reference project).
+ */
+#ifndef TINYTORCH_B200_H
+#define TINYTORCH_B200_H
+
+#include "tensor.h"
+#include "autograd.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- device, stream, errors ---------------------------------------------- */
+/* Number of CUDA devices visible to the process (0 when there is none). */
+int         ttb_device_count(void);
+/* Select the GPU for this process before the first tensor is created.
+ * Without this call the library uses $TT_DEVICE, else $LOCAL_RANK, else 0.
+ * Returns 0, or -1 (see ttb_last_error) when the device cannot be used. */
+int         ttb_init(int device);
+/* Text of the most recent failure ("" when none).  Every entry point that
+ * returns NULL or -1 because of CUDA or NCCL leaves its reason here. */
+const char *ttb_last_error(void);
+/* Wait until everything enqueued so far has finished.  Returns 0 or -1. */
+int         ttb_sync(void);
+/* Kernel launches enqueued by this library since load. */
+long        ttb_launch_count(void);
+/* Device address of a tensor's payload (uploads a pending host write first). */
+float      *ttb_device_ptr(Tensor *t);
+
+/* CUDA-event timing on the library's own stream. */
+void       *ttb_event_create(void);
+void        ttb_event_record(void *ev);
+float       ttb_event_elapsed_ms(void *start, void *stop);   /* waits for `stop` */
+void        ttb_event_destroy(void *ev);
+
+/* Per-kernel-class timing.  While enabled, every launch of the classes below
+ * is bracketed by an event pair; ttb_trace_read waits for the stream and
+ * returns the sums since the last ttb_trace_reset. */
+enum { TTB_K_GEMM_TC = 0, TTB_K_GEMM_SIMT = 1, TTB_K_ELEMENTWISE = 2,
+       TTB_K_SOFTMAX = 3, TTB_K_SPATIAL = 4, TTB_K_REDUCE = 5, TTB_K_OPTIM = 6,
+       TTB_K_COUNT = 7 };
+void        ttb_trace_enable(int on);
+void        ttb_trace_reset(void);
+int         ttb_trace_read(int kind, double *total_ms, long *launches, double *work);
+
+/* ---- GEMM ------------------------------------------------------------------
+ * 0 = choose by shape, 1 = always the tcgen05 3xTF32 kernel (fails when the
+ * shape cannot be fed by TMA), 2 = always the exact-fp32 kernel. */
+void    ttb_set_gemm_path(int path);
+/* Stand-alone forms of the two backward GEMMs the reference keeps private:
+ *   ttb_matmul_nt: R[M,N] = X[M,K] * Y[N,K]^T   (src/autograd.c:66-84)
+ *   ttb_matmul_tn: R[M,N] = X[K,M]^T * Y[K,N]   (src/autograd.c:87-103) */
+Tensor *ttb_matmul_nt(const Tensor *x, const Tensor *y);
+Tensor *ttb_matmul_tn(const Tensor *x, const Tensor *y);
+
+/* ---- backward kernels as operators ----------------------------------------
+ * relu: dx = x > 0 ? g : 0                      (src/autograd.c:318-327)
+ * softmax: dx = s * (g - sum(g*s)) per row      (src/autograd.c:329-346) */
+Tensor *ttb_relu_bwd(const Tensor *x, const Tensor *g);
+Tensor *ttb_softmax_bwd(const Tensor *s, const Tensor *g);
+/* Batched im2col and its adjoint (src/ops_spatial.c:37-69,
+ * src/autograd.c:406-434).  x is [N,C,H,W]; col is [C*kh*kw, N*Hout*Wout]. */
+Tensor *ttb_im2col(const Tensor *x, int kh, int kw, int stride_h, int stride_w,
+                   int pad_h, int pad_w);
+Tensor *ttb_col2im(const Tensor *col, int N, int C, int H, int W, int kh, int kw,
+                   int stride_h, int stride_w, int pad_h, int pad_w);
+/* Max-pool gradient routing (src/autograd.c:555-594).  ttb_maxpool_argmax
+ * writes, for every output element, the flat offset into x that receives its
+ * gradient (host array of Hout*Wout*N*C longs). */
+Tensor *ttb_maxpool_bwd(const Tensor *x, const Tensor *g, int pool_h, int pool_w,
+                        int stride_h, int stride_w);
+int     ttb_maxpool_argmax(const Tensor *x, int pool_h, int pool_w,
+                           int stride_h, int stride_w, long *idx_out);
+Tensor *ttb_avgpool_bwd(const Tensor *g, int N, int C, int H, int W, int pool_h,
+                        int pool_w, int stride_h, int stride_w);
+
+/* ---- fused loss -----------------------------------------------------------
+ * Softmax + cross-entropy + gradient in one pass over the logits.  Stands in
+ * for softmax on the device followed by the NumPy lines of the gate scripts
+ * (tests/gate_mnist_mlp.py:112-119): p = softmax(logits),
+ * loss = mean(-log max(p[y], 1e-12)), dlogits = (p - onehot(y)) * scale.
+ * labels holds the class index of every row as fp32.  *dlogits receives a new
+ * tensor shaped like logits; the return value is a 1-element tensor holding
+ * the mean loss.  NULL on shape errors. */
+Tensor *ttb_softmax_xent(const Tensor *logits, const Tensor *labels, float scale,
+                         Tensor **dlogits);
+
+/* ---- autograd extras ------------------------------------------------------
+ * ag_backward_from with the seed already on the device: same contract, no
+ * host round trip.  Returns 0, or -1 when the element counts differ. */
+int     ag_backward_from_tensor(AGNode *out, const Tensor *seed);
+/* Drop a node's accumulated gradient so that the next pass starts from zero.
+ * Needed once a parameter leaf outlives a step; the reference scripts build
+ * new leaves every step instead (tests/gate_mnist_mlp.py:108-110). */
+void    ag_zero_grad(AGNode *n);
+
+/* ---- optimiser steps on the device ----------------------------------------
+ * In-place forms of the NumPy updates in the gate scripts:
+ *   sgd:       w -= lr * g
+ *   momentum:  v = mu*v - lr*g ; w += v          (tests/gate_mnist_mlp.py:121-124)
+ *   adam:      the update of tests/gate_cifar_cnn.py:81-98, step count t >= 1;
+ *              scalars are doubles because the script's are Python floats
+ * All return 0, or -1 on a shape mismatch. */
+int     ttb_sgd_step(Tensor *w, const Tensor *g, float lr);
+int     ttb_sgd_momentum_step(Tensor *w, Tensor *v, const Tensor *g, float lr, float mu);
+int     ttb_adam_step(Tensor *w, Tensor *m, Tensor *v, const Tensor *g, double lr,
+                      double beta1, double beta2, double eps, int t);
+
+/* ---- data parallel training ----------------------------------------------
+ * One process per GPU.  Rank 0 makes an id with ttb_dist_unique_id, the
+ * launcher hands its 128 bytes to every rank, every rank calls
+ * ttb_dist_init.  A leaf marked with ag_mark_param has its gradient summed
+ * over all ranks (fp32 NCCL all-reduce on a second stream) as soon as the
+ * backward pass has finished accumulating into it, so the reduction overlaps
+ * the rest of the pass; ttb_dist_join makes the compute stream wait for all
+ * reductions in flight.  The reference has no counterpart: it is a
+ * single-process library. */
+int     ttb_dist_unique_id(char id_out[128]);
+int     ttb_dist_init(int rank, int world, const char id[128]);
+int     ttb_dist_world(void);                        /* 1 when not initialised */
+void    ag_mark_param(AGNode *leaf, int on);
+int     ttb_dist_allreduce(Tensor *t);               /* sum over ranks, in place, async */
+int     ttb_dist_join(void);
+void    ttb_dist_finalize(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

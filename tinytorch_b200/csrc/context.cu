@@ -1,0 +1,194 @@
+/* Process-wide device context: one GPU, one compute stream, a stream-ordered
+ * memory pool, the last-error text and per-kernel-class event timing.
+ *
+ * The reference keeps no such state (it is host code over malloc); this file
+ * is what "L0 hardware" becomes once storage moves into HBM. */
+#include "tt_internal.h"
+
+#include <stdarg.h>
+#include <stdlib.h>
+#include <string.h>
+
+TTContext g_tt = {0, 0, 0, nullptr, nullptr, 0, 1, 0, 0};
+
+static char g_err[512] = "";
+
+void tt_set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    if (getenv("TT_VERBOSE")) fprintf(stderr, "tinytorch-b200: %s\n", g_err);
+}
+
+int tt_cuda_ok(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return 1;
+    tt_set_error("%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+static int env_int(const char *name, int dflt) {
+    const char *s = getenv(name);
+    if (!s || !*s) return dflt;
+    return atoi(s);
+}
+
+static int ctx_open(int device) {
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count <= 0) {
+        tt_set_error("no CUDA device available (%s): this library has no CPU path",
+                     e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+        g_tt.ready = -1;
+        return -1;
+    }
+    if (device < 0 || device >= count) {
+        tt_set_error("device %d out of range (%d visible)", device, count);
+        g_tt.ready = -1;
+        return -1;
+    }
+    if (!tt_cuda_ok(cudaSetDevice(device), "cudaSetDevice")) { g_tt.ready = -1; return -1; }
+    cudaDeviceProp prop;
+    if (!tt_cuda_ok(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) { g_tt.ready = -1; return -1; }
+    if (prop.major != 10) {
+        tt_set_error("device %d is sm_%d%d; this library carries sm_100a code only",
+                     device, prop.major, prop.minor);
+        g_tt.ready = -1;
+        return -1;
+    }
+    g_tt.device = device;
+    g_tt.sm_count = prop.multiProcessorCount;
+    if (!tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.stream, cudaStreamNonBlocking), "cudaStreamCreate") ||
+        !tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.comm_stream, cudaStreamNonBlocking), "cudaStreamCreate")) {
+        g_tt.ready = -1;
+        return -1;
+    }
+    /* Keep freed blocks in the pool: the training loop allocates the same
+     * sizes every step and must not go back to the driver for them. */
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+        unsigned long long keep = ~0ull;
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    g_tt.gemm_path = env_int("TT_GEMM_PATH", 0);
+    g_tt.fuse_padones = env_int("TT_FUSE_PADONES", 1);
+    g_tt.ready = 1;
+    return 0;
+}
+
+int tt_ctx_init(void) {
+    if (g_tt.ready == 1) return 0;
+    if (g_tt.ready == -1) return -1;
+    int dev = env_int("TT_DEVICE", env_int("LOCAL_RANK", 0));
+    return ctx_open(dev);
+}
+
+extern "C" int ttb_device_count(void) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return count;
+}
+
+extern "C" int ttb_init(int device) {
+    if (g_tt.ready == 1) {
+        if (device == g_tt.device) return 0;
+        tt_set_error("ttb_init(%d): the library already runs on device %d", device, g_tt.device);
+        return -1;
+    }
+    g_tt.ready = 0;
+    return ctx_open(device);
+}
+
+extern "C" const char *ttb_last_error(void) { return g_err; }
+
+extern "C" int ttb_sync(void) {
+    if (tt_ctx_init() != 0) return -1;
+    if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.stream), "cudaStreamSynchronize")) return -1;
+    if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.comm_stream), "cudaStreamSynchronize(comm)")) return -1;
+    return 0;
+}
+
+extern "C" long ttb_launch_count(void) { return g_tt.launches; }
+
+void *tt_dev_alloc(size_t bytes) {
+    if (tt_ctx_init() != 0) return nullptr;
+    void *p = nullptr;
+    if (bytes == 0) bytes = 4;
+    if (!tt_cuda_ok(cudaMallocAsync(&p, bytes, g_tt.stream), "cudaMallocAsync")) return nullptr;
+    return p;
+}
+
+void tt_dev_free(void *p) {
+    if (!p || g_tt.ready != 1) return;
+    cudaFreeAsync(p, g_tt.stream);
+}
+
+/* ---- events ---------------------------------------------------------------*/
+extern "C" void *ttb_event_create(void) {
+    if (tt_ctx_init() != 0) return nullptr;
+    cudaEvent_t ev;
+    if (!tt_cuda_ok(cudaEventCreate(&ev), "cudaEventCreate")) return nullptr;
+    return (void *)ev;
+}
+extern "C" void ttb_event_record(void *ev) {
+    if (ev && g_tt.ready == 1) cudaEventRecord((cudaEvent_t)ev, g_tt.stream);
+}
+extern "C" float ttb_event_elapsed_ms(void *a, void *b) {
+    float ms = -1.0f;
+    if (!a || !b) return ms;
+    if (!tt_cuda_ok(cudaEventSynchronize((cudaEvent_t)b), "cudaEventSynchronize")) return -1.0f;
+    if (!tt_cuda_ok(cudaEventElapsedTime(&ms, (cudaEvent_t)a, (cudaEvent_t)b), "cudaEventElapsedTime")) return -1.0f;
+    return ms;
+}
+extern "C" void ttb_event_destroy(void *ev) { if (ev) cudaEventDestroy((cudaEvent_t)ev); }
+
+/* ---- per-class tracing ----------------------------------------------------
+ * Event pairs come from a growing pool and are resolved when read. */
+typedef struct TracePair { cudaEvent_t a, b; int kind; double work; } TracePair;
+static TracePair *g_pairs = nullptr;
+static long g_npairs = 0, g_cap_pairs = 0, g_made_pairs = 0;
+
+extern "C" void ttb_trace_enable(int on) { g_tt.trace = on ? 1 : 0; }
+extern "C" void ttb_trace_reset(void) { g_npairs = 0; }
+
+void tt_trace_begin(int kind) {
+    if (!g_tt.trace) return;
+    if (g_npairs == g_cap_pairs) {
+        long nc = g_cap_pairs ? g_cap_pairs * 2 : 1024;
+        TracePair *np = (TracePair *)realloc(g_pairs, sizeof(TracePair) * (size_t)nc);
+        if (!np) { g_tt.trace = 0; return; }
+        g_pairs = np; g_cap_pairs = nc;
+    }
+    TracePair *p = &g_pairs[g_npairs];
+    if (g_npairs >= g_made_pairs) {
+        if (cudaEventCreate(&p->a) != cudaSuccess || cudaEventCreate(&p->b) != cudaSuccess) { g_tt.trace = 0; return; }
+        g_made_pairs = g_npairs + 1;
+    }
+    p->kind = kind;
+    cudaEventRecord(p->a, g_tt.stream);
+}
+
+void tt_trace_end(int kind, double work) {
+    if (!g_tt.trace) return;
+    TracePair *p = &g_pairs[g_npairs];
+    (void)kind;
+    p->work = work;
+    cudaEventRecord(p->b, g_tt.stream);
+    g_npairs++;
+}
+
+extern "C" int ttb_trace_read(int kind, double *total_ms, long *launches, double *work) {
+    if (g_tt.ready != 1) return -1;
+    if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.stream), "cudaStreamSynchronize")) return -1;
+    double t = 0.0, w = 0.0; long n = 0;
+    for (long i = 0; i < g_npairs; i++) {
+        if (g_pairs[i].kind != kind) continue;
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, g_pairs[i].a, g_pairs[i].b) != cudaSuccess) continue;
+        t += ms; w += g_pairs[i].work; n++;
+    }
+    if (total_ms) *total_ms = t;
+    if (launches) *launches = n;
+    if (work) *work = w;
+    return 0;
+}

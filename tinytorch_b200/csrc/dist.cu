@@ -1,0 +1,157 @@
+/* Data-parallel gradient reduction over NCCL (NVLink 5 / NVSwitch).
+ *
+ * The reference is a single-process library with no communication layer;
+ * this file is new.  One process drives one GPU and holds a full replica of
+ * the parameters; the batch is split by rows and every rank's loss seed is
+ * scaled by 1/global_batch, so a SUM all-reduce of each parameter gradient
+ * reproduces the full-batch gradient.  The reduction of a gradient is
+ * enqueued on a second stream the moment the backward pass has finished
+ * accumulating into it (see run_backward in autograd.cu), ordered after the
+ * producing kernels by an event, and overlaps the remaining backward GEMMs.
+ *
+ * NCCL is bound at run time with dlopen, so the library loads and the
+ * single-GPU path works on a machine without NCCL, and a process that has
+ * already loaded an NCCL (for instance through PyTorch) shares that copy
+ * instead of pulling in a second one.  Failures are reported, never waited
+ * on: the communicator is created in blocking mode, every call's result is
+ * checked, and ttb_dist_join polls ncclCommGetAsyncError. */
+#include "tt_internal.h"
+
+#include <dlfcn.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* The handful of NCCL declarations this file needs (public API, nccl.h). */
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+typedef int ncclResult_t;          /* 0 = ncclSuccess, 7 = ncclInProgress */
+enum { NCCL_FLOAT32 = 7, NCCL_SUM = 0 };
+
+typedef ncclResult_t (*fn_GetUniqueId)(ncclUniqueId *);
+typedef ncclResult_t (*fn_CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
+typedef ncclResult_t (*fn_AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t);
+typedef ncclResult_t (*fn_CommDestroy)(ncclComm_t);
+typedef ncclResult_t (*fn_CommAbort)(ncclComm_t);
+typedef ncclResult_t (*fn_CommGetAsyncError)(ncclComm_t, ncclResult_t *);
+typedef const char *(*fn_GetErrorString)(ncclResult_t);
+
+static struct {
+    void *handle;
+    fn_GetUniqueId GetUniqueId;
+    fn_CommInitRank CommInitRank;
+    fn_AllReduce AllReduce;
+    fn_CommDestroy CommDestroy;
+    fn_CommAbort CommAbort;
+    fn_CommGetAsyncError CommGetAsyncError;
+    fn_GetErrorString GetErrorString;
+} nccl;
+
+static ncclComm_t g_comm = nullptr;
+static int g_world = 1, g_rank = 0;
+static cudaEvent_t g_ev_ready = nullptr, g_ev_done = nullptr;
+static int g_inflight = 0;
+
+static int nccl_bind(void) {
+    if (nccl.handle) return 0;
+    const char *names[] = {getenv("TT_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    for (int i = 0; i < 3 && !nccl.handle; i++)
+        if (names[i] && *names[i]) nccl.handle = dlopen(names[i], RTLD_NOW | RTLD_GLOBAL);
+    if (!nccl.handle) { tt_set_error("NCCL not found (dlopen libnccl.so.2): %s", dlerror()); return -1; }
+    nccl.GetUniqueId = (fn_GetUniqueId)dlsym(nccl.handle, "ncclGetUniqueId");
+    nccl.CommInitRank = (fn_CommInitRank)dlsym(nccl.handle, "ncclCommInitRank");
+    nccl.AllReduce = (fn_AllReduce)dlsym(nccl.handle, "ncclAllReduce");
+    nccl.CommDestroy = (fn_CommDestroy)dlsym(nccl.handle, "ncclCommDestroy");
+    nccl.CommAbort = (fn_CommAbort)dlsym(nccl.handle, "ncclCommAbort");
+    nccl.CommGetAsyncError = (fn_CommGetAsyncError)dlsym(nccl.handle, "ncclCommGetAsyncError");
+    nccl.GetErrorString = (fn_GetErrorString)dlsym(nccl.handle, "ncclGetErrorString");
+    if (!nccl.GetUniqueId || !nccl.CommInitRank || !nccl.AllReduce || !nccl.CommDestroy ||
+        !nccl.CommAbort || !nccl.CommGetAsyncError || !nccl.GetErrorString) {
+        tt_set_error("NCCL library lacks a required symbol");
+        dlclose(nccl.handle);
+        memset(&nccl, 0, sizeof nccl);
+        return -1;
+    }
+    return 0;
+}
+
+static int nccl_ok(ncclResult_t r, const char *what) {
+    if (r == 0) return 1;
+    tt_set_error("%s: %s", what, nccl.GetErrorString ? nccl.GetErrorString(r) : "NCCL error");
+    return 0;
+}
+
+extern "C" int ttb_dist_unique_id(char id_out[128]) {
+    if (!id_out) return -1;
+    if (nccl_bind() != 0) return -1;
+    ncclUniqueId id;
+    if (!nccl_ok(nccl.GetUniqueId(&id), "ncclGetUniqueId")) return -1;
+    memcpy(id_out, id.internal, 128);
+    return 0;
+}
+
+extern "C" int ttb_dist_init(int rank, int world, const char id_in[128]) {
+    if (g_comm) { tt_set_error("ttb_dist_init: already initialised"); return -1; }
+    if (world < 1 || rank < 0 || rank >= world || !id_in) { tt_set_error("ttb_dist_init: bad rank/world"); return -1; }
+    if (tt_ctx_init() != 0) return -1;
+    if (world == 1) { g_world = 1; g_rank = 0; return 0; }
+    if (nccl_bind() != 0) return -1;
+    ncclUniqueId id;
+    memcpy(id.internal, id_in, 128);
+    if (!nccl_ok(nccl.CommInitRank(&g_comm, world, id, rank), "ncclCommInitRank")) { g_comm = nullptr; return -1; }
+    if (!tt_cuda_ok(cudaEventCreateWithFlags(&g_ev_ready, cudaEventDisableTiming), "cudaEventCreate") ||
+        !tt_cuda_ok(cudaEventCreateWithFlags(&g_ev_done, cudaEventDisableTiming), "cudaEventCreate")) return -1;
+    g_world = world; g_rank = rank;
+    return 0;
+}
+
+extern "C" int ttb_dist_world(void) { return g_world; }
+int tt_dist_active(void) { return g_comm != nullptr && g_world > 1; }
+
+/* Sum `t` over all ranks in place.  Ordered after everything already on the
+ * compute stream; runs on the communication stream. */
+int tt_dist_allreduce_async(Tensor *t) {
+    if (!tt_dist_active()) return 0;
+    float *p = tt_dev_rw(t);
+    if (!p) return -1;
+    if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
+        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
+    if (!nccl_ok(nccl.AllReduce(p, p, (size_t)t->numel, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream),
+                 "ncclAllReduce")) return -1;
+    g_inflight++;
+    return 0;
+}
+
+extern "C" int ttb_dist_allreduce(Tensor *t) {
+    if (!t) return -1;
+    return tt_dist_allreduce_async(t);
+}
+
+/* Make the compute stream wait for every reduction enqueued so far. */
+extern "C" int ttb_dist_join(void) {
+    if (!tt_dist_active()) return 0;
+    if (g_inflight) {
+        if (!tt_cuda_ok(cudaEventRecord(g_ev_done, g_tt.comm_stream), "cudaEventRecord") ||
+            !tt_cuda_ok(cudaStreamWaitEvent(g_tt.stream, g_ev_done, 0), "cudaStreamWaitEvent")) return -1;
+        g_inflight = 0;
+    }
+    ncclResult_t async = 0;
+    if (!nccl_ok(nccl.CommGetAsyncError(g_comm, &async), "ncclCommGetAsyncError")) return -1;
+    if (async != 0 && async != 7) {
+        nccl_ok(async, "NCCL asynchronous error");
+        nccl.CommAbort(g_comm);
+        g_comm = nullptr; g_world = 1;
+        return -1;
+    }
+    return 0;
+}
+
+extern "C" void ttb_dist_finalize(void) {
+    if (g_comm) {
+        cudaStreamSynchronize(g_tt.comm_stream);
+        nccl.CommDestroy(g_comm);
+        g_comm = nullptr;
+    }
+    if (g_ev_ready) { cudaEventDestroy(g_ev_ready); g_ev_ready = nullptr; }
+    if (g_ev_done) { cudaEventDestroy(g_ev_done); g_ev_done = nullptr; }
+    g_world = 1; g_rank = 0; g_inflight = 0;
+}

@@ -1,0 +1,478 @@
+/* Tensor-core GEMM for sm_100a: tcgen05.mma kind::tf32 in a 3xTF32 split,
+ * TMA-staged operand tiles, accumulators in tensor memory.
+ *
+ * Replaces the reference's blocked AVX2 sgemm (src/gemm.c:569-641) and its
+ * two naive backward products dA = dC*B^T and dB = A^T*dC
+ * (src/autograd.c:66-103).  No operand is ever transposed in memory: an
+ * operand whose reduction index is not the contiguous one is loaded as an
+ * "MN-major" tile and the instruction descriptor says so.
+ *
+ *   D[M,N] (+)= A_op[M,K] * B_op[K,N] (+ bias[n])
+ *
+ * Precision.  kind::tf32 reads 32-bit words and uses the top 19 bits.  Each
+ * fp32 operand x is therefore split as hi = x with the low 13 mantissa bits
+ * cleared (what the instruction sees when it is handed x itself) and
+ * lo = x - hi (exact in fp32, rounded to tf32), and every K step issues
+ *   D += A_lo*B_hi;  D += A_hi*B_lo;  D += A_hi*B_hi
+ * into one fp32 accumulator.  The dropped A_lo*B_lo term is below 2^-20
+ * relative, so products carry about 21 bits, which is what "fp32-grade"
+ * means for this kernel.
+ *
+ * Structure of one CTA (persistent, one per SM, 320 threads):
+ *   warp 0      TMA producer: cp.async.bulk.tensor loads (no multicast) of
+ *               the raw A and B tiles of a K block into a ring of stages.
+ *   warps 2-5   split: read the raw tiles from shared memory, write the lo
+ *               tiles next to them at the same (swizzled) offsets.
+ *   warp 1      one thread issues the tcgen05.mma triples and commits to
+ *               mbarriers; owns the tensor-memory allocation.
+ *   warps 6-9   epilogue: tcgen05.ld the finished accumulator (one of two,
+ *               so the next tile's MMAs overlap), add bias / old C, store.
+ * Tile 128 x BN x 32 (BN = 256 or 128), SWIZZLE_128B everywhere.
+ *
+ * Every wait is bounded: a wait that exceeds its cycle budget records a code
+ * in a host-visible status word, raises a CTA-wide abort flag that all other
+ * waits poll, and the CTA drains, frees its tensor memory and exits. */
+#include "tt_internal.h"
+
+#include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define TC_BM 128
+#define TC_BK 32                 /* 32 fp32 = one 128-byte swizzle span */
+#define TC_THREADS 320
+#define TC_SPLIT_THREADS 128
+#define TC_EPI_THREADS 128
+#define TC_WAIT_CYCLES (1ll << 30)
+
+/* ---- small PTX wrappers ---------------------------------------------------*/
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+/* Bounded wait.  Returns false when the budget ran out here or elsewhere in the CTA. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t *status, uint32_t code) {
+    if (mbar_try(bar, parity)) return true;
+    long long t0 = clock64();
+    for (;;) {
+        #pragma unroll 1
+        for (int i = 0; i < 16; i++)
+            if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TC_WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(status, 0u, code | (blockIdx.x << 8));
+            __threadfence_system();
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+/* Shared-memory matrix descriptor (64 bit): start address, leading and stride
+ * byte offsets in 16-byte units, version 1, SWIZZLE_128B.
+ *   K-major tile  : rows of 128 bytes, 8-row groups 1024 bytes apart (stride
+ *                   offset); a K step of 8 fp32 advances the start by 32 bytes.
+ *   MN-major tile : built from boxes of 32 k-rows x 128 bytes (32 values along
+ *                   M or N); boxes 4096 bytes apart (leading offset), 8-row
+ *                   groups 1024 bytes apart; a K step advances by 1024 bytes. */
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;            /* descriptor version for sm_100 */
+    d |= (uint64_t)2 << 61;            /* SWIZZLE_128B */
+    return d;
+}
+
+/* lo part of the 3xTF32 split: x minus its 19-bit truncation, rounded to tf32. */
+__device__ __forceinline__ float split_lo(float x) {
+    float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    float lo = x - hi;
+    if (fabsf(x) == INFINITY) lo = 0.0f;       /* keep Inf an Inf instead of Inf - Inf */
+    return __uint_as_float((__float_as_uint(lo) + 0x1000u) & 0xffffe000u);
+}
+
+struct TcParams {
+    int M, N, K;
+    float *C; long ldc;
+    const float *bias;
+    int accumulate;
+    int passes;              /* 3 = full split, 1 = hi*hi only (bring-up aid) */
+    uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
+};
+
+template <int A_MN, int B_MN, int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 4;          /* 16 KB */
+    constexpr uint32_t B_BYTES = BN * TC_BK * 4;
+    constexpr uint32_t HI_BYTES = A_BYTES + B_BYTES;         /* raw tiles of one stage */
+    constexpr uint32_t STAGE_BYTES = 2 * HI_BYTES;           /* raw + lo */
+    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)A_MN << 15) |
+                               ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+    constexpr uint32_t TMEM_COLS = 2 * BN;                   /* two accumulators */
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    /* control block after the stages */
+    uint64_t *bars = (uint64_t *)(smem_gen + STAGES * STAGE_BYTES);
+    const uint32_t bar_full = smem_u32(bars);                         /* STAGES */
+    const uint32_t bar_lo = bar_full + 8 * STAGES;                    /* STAGES */
+    const uint32_t bar_empty = bar_lo + 8 * STAGES;                   /* STAGES */
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES;                /* 2 */
+    const uint32_t bar_tempty = bar_tfull + 16;                       /* 2 */
+    uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 4);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + TC_BM - 1) / TC_BM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_lo + 8 * s, TC_SPLIT_THREADS);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, TC_EPI_THREADS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        /* ---------------- TMA producer ---------------- */
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
+                    const uint32_t st = smem_base + s * STAGE_BYTES;
+                    const uint32_t full = bar_full + 8 * s;
+                    mbar_expect_tx(full, HI_BYTES);
+                    const int k0 = kb * TC_BK;
+                    if (A_MN) {
+                        #pragma unroll
+                        for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * 4096, &map_a, full, m0 + 32 * b, k0);
+                    } else {
+                        tma_load_2d(st, &map_a, full, k0, m0);
+                    }
+                    if (B_MN) {
+                        #pragma unroll
+                        for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * 4096, &map_b, full, n0 + 32 * b, k0);
+                    } else {
+                        tma_load_2d(st + A_BYTES, &map_b, full, k0, n0);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+            if (!ok) {
+                /* give loads already in flight time to land before the CTA exits */
+                long long t0 = clock64();
+                while (clock64() - t0 < 200000) { }
+            }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issuer ---------------- */
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 4)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_lo + 8 * s, ph, abort_flag, p.status, 2) ||
+                        !mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_hi = smem_base + s * STAGE_BYTES;
+                    const uint32_t b_hi = a_hi + A_BYTES;
+                    const uint32_t a_lo = a_hi + HI_BYTES;
+                    const uint32_t b_lo = b_hi + HI_BYTES;
+                    #pragma unroll
+                    for (int ks = 0; ks < TC_BK / 8; ks++) {
+                        const uint32_t a_off = A_MN ? ks * 1024 : ks * 32;
+                        const uint32_t b_off = B_MN ? ks * 1024 : ks * 32;
+                        const uint32_t a_lbo = A_MN ? 4096 : 16, b_lbo = B_MN ? 4096 : 16;
+                        const uint64_t da_hi = make_desc(a_hi + a_off, a_lbo, 1024);
+                        const uint64_t db_hi = make_desc(b_hi + b_off, b_lbo, 1024);
+                        const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
+                        if (p.passes == 3) {
+                            const uint64_t da_lo = make_desc(a_lo + a_off, a_lbo, 1024);
+                            const uint64_t db_lo = make_desc(b_lo + b_off, b_lbo, 1024);
+                            tc_mma_tf32(d_tmem, da_lo, db_hi, IDESC, first);
+                            tc_mma_tf32(d_tmem, da_hi, db_lo, IDESC, 1u);
+                            tc_mma_tf32(d_tmem, da_hi, db_hi, IDESC, 1u);
+                        } else {
+                            tc_mma_tf32(d_tmem, da_hi, db_hi, IDESC, first);
+                        }
+                    }
+                    tc_commit(bar_empty + 8 * s);      /* stage reusable once these MMAs have read it */
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit(bar_tfull + 8 * acc);        /* accumulator complete */
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+    } else if (warp < 6) {
+        /* ---------------- split warps: lo = x - trunc19(x) ---------------- */
+        const int st_tid = threadIdx.x - 64;
+        int s = 0; uint32_t ph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int kb = 0; kb < num_kb; kb++) {
+                const bool got = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 1);
+                if (!__all_sync(0xffffffffu, got)) { ok = false; break; }     /* keep the warp together */
+                if (p.passes == 3) {
+                    const uint8_t *hi = smem_gen + s * STAGE_BYTES;
+                    #pragma unroll 4
+                    for (uint32_t c = st_tid; c < HI_BYTES / 16; c += TC_SPLIT_THREADS) {
+                        float4 v = *(const float4 *)(hi + c * 16);
+                        float4 w = make_float4(split_lo(v.x), split_lo(v.y), split_lo(v.z), split_lo(v.w));
+                        *(float4 *)(hi + HI_BYTES + c * 16) = w;
+                    }
+                    /* make the generic-proxy writes visible to the tensor core's reads */
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                mbar_arrive(bar_lo + 8 * s);
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+    } else {
+        /* ---------------- epilogue warps ---------------- */
+        const int q = warp & 3;                       /* tensor-memory lane quarter this warp may read */
+        int acc = 0; uint32_t acc_ph = 0;
+        bool ok = true;
+        const bool vec_ok = ((p.ldc & 3) == 0) && ((((uintptr_t)p.C) & 15u) == 0);
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
+            const bool got = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }         /* tcgen05.ld needs the whole warp */
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            float *crow = p.C + (long)row * p.ldc;
+            #pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                tc_wait_ld();
+                if (c0 + 32 >= BN) {
+                    /* last read of this accumulator: hand it back before the stores */
+                    tc_fence_before();
+                    mbar_arrive(bar_tempty + 8 * acc);
+                }
+                const int gc = n0 + c0;
+                if (row < p.M && gc < p.N) {
+                    if (vec_ok && gc + 32 <= p.N) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            if (p.bias) {
+                                v.x += p.bias[gc + j]; v.y += p.bias[gc + j + 1];
+                                v.z += p.bias[gc + j + 2]; v.w += p.bias[gc + j + 3];
+                            }
+                            if (p.accumulate) {
+                                float4 o = *(const float4 *)(crow + gc + j);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *(float4 *)(crow + gc + j) = v;
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (gc + j < p.N) {
+                                float v = __uint_as_float(r[j]);
+                                if (p.bias) v += p.bias[gc + j];
+                                if (p.accumulate) v += crow[gc + j];
+                                crow[gc + j] = v;
+                            }
+                        }
+                    }
+                }
+            }
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+/* ---- host side ----------------------------------------------------------------*/
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static uint32_t *g_status_host = nullptr;     /* mapped pinned word the kernel reports into */
+static uint32_t *g_status_dev = nullptr;
+static int g_tc_passes = 3;
+
+static int tc_setup(void) {
+    if (g_encode && g_status_host) return 0;
+    if (tt_ctx_init() != 0) return -1;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (!tt_cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint") ||
+        qres != cudaDriverEntryPointSuccess || !fn) {
+        tt_set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return -1;
+    }
+    g_encode = (EncodeTiledFn)fn;
+    if (!tt_cuda_ok(cudaHostAlloc((void **)&g_status_host, sizeof(uint32_t), cudaHostAllocMapped), "cudaHostAlloc")) return -1;
+    *g_status_host = 0;
+    if (!tt_cuda_ok(cudaHostGetDevicePointer((void **)&g_status_dev, g_status_host, 0), "cudaHostGetDevicePointer")) return -1;
+    const char *e = getenv("TT_TC_PASSES");
+    if (e && atoi(e) == 1) g_tc_passes = 1;
+    return 0;
+}
+
+/* Non-zero when a tensor-core kernel gave up on a wait since the last call. */
+int gemm_tc_poll_status(void) {
+    if (!g_status_host) return 0;
+    uint32_t v = *(volatile uint32_t *)g_status_host;
+    if (v) {
+        tt_set_error("tcgen05 GEMM: bounded wait expired (code %u, CTA %u)", v & 0xffu, v >> 8);
+        *g_status_host = 0;
+        return (int)v;
+    }
+    return 0;
+}
+
+/* inner = contiguous extent, outer = number of rows, pitch in floats */
+static int encode_map(CUtensorMap *map, const float *base, long inner, long outer, long pitch, int box_inner, int box_outer) {
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { tt_set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return -1; }
+    return 0;
+}
+
+int gemm_tc_usable(const GemmArgs *g) {
+    if (g->a_pad_ones) return 0;
+    if (g->M <= 0 || g->N <= 0 || g->K <= 0) return 0;
+    if ((((uintptr_t)g->A) & 15u) || (((uintptr_t)g->B) & 15u)) return 0;
+    if ((g->lda & 3) || (g->ldb & 3)) return 0;
+    if (g->lda >= (1l << 36) || g->ldb >= (1l << 36)) return 0;
+    return 1;
+}
+
+template <int A_MN, int B_MN, int BN, int STAGES>
+static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb) {
+    constexpr size_t smem = (size_t)STAGES * 2 * (TC_BM * TC_BK * 4 + BN * TC_BK * 4) + 1024 + 8 * (3 * STAGES + 4) + 16;
+    static bool configured = false;
+    auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES>;
+    if (!configured) {
+        if (!tt_cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                        "cudaFuncSetAttribute(smem)")) return -1;
+        configured = true;
+    }
+    TcParams p;
+    p.M = g->M; p.N = g->N; p.K = g->K; p.C = g->C; p.ldc = g->ldc; p.bias = g->bias;
+    p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev;
+    int tiles = ((g->M + TC_BM - 1) / TC_BM) * ((g->N + BN - 1) / BN);
+    int grid = tiles < g_tt.sm_count ? tiles : g_tt.sm_count;
+    tt_trace_begin(TTB_K_GEMM_TC);
+    kern<<<grid, TC_THREADS, smem, g_tt.stream>>>(ma, mb, p);
+    g_tt.launches++;
+    tt_trace_end(TTB_K_GEMM_TC, 2.0 * (double)g->M * g->N * g->K);
+    return tt_cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch") ? 0 : -1;
+}
+
+template <int BN, int STAGES>
+static int launch_tc_major(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb) {
+    const int a_mn = g->ta ? 1 : 0, b_mn = g->tb ? 0 : 1;
+    if (!a_mn && !b_mn) return launch_tc<0, 0, BN, STAGES>(g, ma, mb);
+    if (!a_mn && b_mn)  return launch_tc<0, 1, BN, STAGES>(g, ma, mb);
+    if (a_mn && !b_mn)  return launch_tc<1, 0, BN, STAGES>(g, ma, mb);
+    return launch_tc<1, 1, BN, STAGES>(g, ma, mb);
+}
+
+int gemm_tc(const GemmArgs *g) {
+    if (!gemm_tc_usable(g)) { tt_set_error("tcgen05 GEMM: operands are not 16-byte aligned with 16-byte row pitch"); return -1; }
+    if (tc_setup() != 0) return -1;
+    /* 128x256 tiles unless that leaves most SMs idle */
+    const long tiles256 = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + 255) / 256);
+    const int bn = (tiles256 * 10 < (long)g_tt.sm_count * 7 || g->N <= 128) ? 128 : 256;
+    CUtensorMap ma, mb;
+    if (g->ta) { if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, 32)) return -1; }
+    else       { if (encode_map(&ma, g->A, g->K, g->M, g->lda, TC_BK, TC_BM)) return -1; }
+    if (g->tb) { if (encode_map(&mb, g->B, g->K, g->N, g->ldb, TC_BK, bn)) return -1; }
+    else       { if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, 32)) return -1; }
+    if (bn == 256) return launch_tc_major<256, 2>(g, ma, mb);
+    return launch_tc_major<128, 3>(g, ma, mb);
+}

@@ -1,0 +1,470 @@
+/* Memory-bound kernels of the hot path: elementwise operators, relu and its
+ * gradient, padones and its adjoint, softmax forward/backward, the fused
+ * softmax-cross-entropy gradient, column sums, optimiser steps, transpose.
+ *
+ * All of them are HBM-bound streaming kernels: 128-bit loads and stores where
+ * the pointers allow it, several independent loads in flight per thread, a
+ * grid of a whole number of waves (blocks = SMs x resident blocks per SM)
+ * walked with a grid-stride loop, and warp-shuffle reductions for the row
+ * operators.  Each kernel names the reference loop it replaces. */
+#include "tt_internal.h"
+
+#include <math.h>
+
+#define TPB 256
+
+static inline int grid_for(long items, int per_sm = 8) {
+    long want = (items + TPB - 1) / TPB;
+    long cap = (long)g_tt.sm_count * per_sm;
+    if (want < 1) want = 1;
+    return (int)(want < cap ? want : cap);
+}
+
+static inline bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
+
+#define LAUNCH(kern, grid, block, smem, ...)                         \
+    do {                                                             \
+        kern<<<(grid), (block), (smem), g_tt.stream>>>(__VA_ARGS__); \
+        g_tt.launches++;                                             \
+    } while (0)
+
+/* ---- generic streaming maps ----------------------------------------------
+ * OP is a functor over scalars; the vector body handles four at a time and
+ * keeps two float4 loads per operand in flight. */
+template <class OP>
+__global__ void __launch_bounds__(TPB) map1_v4(float4 *o, const float4 *a, long n4, OP op) {
+    long stride = (long)gridDim.x * blockDim.x;
+    long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + stride < n4; i += 2 * stride) {
+        float4 x = a[i], y = a[i + stride];
+        o[i] = make_float4(op(x.x), op(x.y), op(x.z), op(x.w));
+        o[i + stride] = make_float4(op(y.x), op(y.y), op(y.z), op(y.w));
+    }
+    if (i < n4) {
+        float4 x = a[i];
+        o[i] = make_float4(op(x.x), op(x.y), op(x.z), op(x.w));
+    }
+}
+template <class OP>
+__global__ void __launch_bounds__(TPB) map1_s(float *o, const float *a, long lo, long n, OP op) {
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = lo + (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = op(a[i]);
+}
+template <class OP>
+__global__ void __launch_bounds__(TPB) map2_v4(float4 *o, const float4 *a,
+                                                const float4 *__restrict__ b, long n4, OP op) {
+    long stride = (long)gridDim.x * blockDim.x;
+    long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + stride < n4; i += 2 * stride) {
+        float4 x = a[i], y = b[i], x2 = a[i + stride], y2 = b[i + stride];
+        o[i] = make_float4(op(x.x, y.x), op(x.y, y.y), op(x.z, y.z), op(x.w, y.w));
+        o[i + stride] = make_float4(op(x2.x, y2.x), op(x2.y, y2.y), op(x2.z, y2.z), op(x2.w, y2.w));
+    }
+    if (i < n4) {
+        float4 x = a[i], y = b[i];
+        o[i] = make_float4(op(x.x, y.x), op(x.y, y.y), op(x.z, y.z), op(x.w, y.w));
+    }
+}
+template <class OP>
+__global__ void __launch_bounds__(TPB) map2_s(float *o, const float *a,
+                                               const float *__restrict__ b, long lo, long n, OP op) {
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = lo + (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = op(a[i], b[i]);
+}
+template <class OP>
+__global__ void __launch_bounds__(TPB) map3_v4(float4 *o, const float4 *a,
+                                                const float4 *__restrict__ b, const float4 *__restrict__ c,
+                                                long n4, OP op) {
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 x = a[i], y = b[i], z = c[i];
+        o[i] = make_float4(op(x.x, y.x, z.x), op(x.y, y.y, z.y), op(x.z, y.z, z.z), op(x.w, y.w, z.w));
+    }
+}
+template <class OP>
+__global__ void __launch_bounds__(TPB) map3_s(float *o, const float *a,
+                                               const float *__restrict__ b, const float *__restrict__ c,
+                                               long lo, long n, OP op) {
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = lo + (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = op(a[i], b[i], c[i]);
+}
+
+template <class OP>
+static void run_map1(float *o, const float *a, long n, OP op) {
+    if (n <= 0) return;
+    tt_trace_begin(TTB_K_ELEMENTWISE);
+    long n4 = (aligned16(o) && aligned16(a)) ? n / 4 : 0;
+    if (n4 > 0) LAUNCH((map1_v4<OP>), grid_for((n4 + 1) / 2), TPB, 0, (float4 *)o, (const float4 *)a, n4, op);
+    if (n4 * 4 < n) LAUNCH((map1_s<OP>), grid_for(n - n4 * 4), TPB, 0, o, a, n4 * 4, n, op);
+    tt_trace_end(TTB_K_ELEMENTWISE, 8.0 * (double)n);
+}
+template <class OP>
+static void run_map2(float *o, const float *a, const float *b, long n, OP op) {
+    if (n <= 0) return;
+    tt_trace_begin(TTB_K_ELEMENTWISE);
+    long n4 = (aligned16(o) && aligned16(a) && aligned16(b)) ? n / 4 : 0;
+    if (n4 > 0) LAUNCH((map2_v4<OP>), grid_for((n4 + 1) / 2), TPB, 0, (float4 *)o, (const float4 *)a, (const float4 *)b, n4, op);
+    if (n4 * 4 < n) LAUNCH((map2_s<OP>), grid_for(n - n4 * 4), TPB, 0, o, a, b, n4 * 4, n, op);
+    tt_trace_end(TTB_K_ELEMENTWISE, 12.0 * (double)n);
+}
+template <class OP>
+static void run_map3(float *o, const float *a, const float *b, const float *c, long n, OP op) {
+    if (n <= 0) return;
+    tt_trace_begin(TTB_K_ELEMENTWISE);
+    long n4 = (aligned16(o) && aligned16(a) && aligned16(b) && aligned16(c)) ? n / 4 : 0;
+    if (n4 > 0) LAUNCH((map3_v4<OP>), grid_for(n4), TPB, 0, (float4 *)o, (const float4 *)a, (const float4 *)b, (const float4 *)c, n4, op);
+    if (n4 * 4 < n) LAUNCH((map3_s<OP>), grid_for(n - n4 * 4), TPB, 0, o, a, b, c, n4 * 4, n, op);
+    tt_trace_end(TTB_K_ELEMENTWISE, 16.0 * (double)n);
+}
+
+/* ---- functors -------------------------------------------------------------*/
+struct OpFill    { float v; __device__ float operator()(float) const { return v; } };
+struct OpCopy    { __device__ float operator()(float x) const { return x; } };
+struct OpAddS    { float s; __device__ float operator()(float x) const { return x + s; } };
+struct OpMulS    { float s; __device__ float operator()(float x) const { return x * s; } };
+/* x > 0 ? x : 0 -- a NaN compares false and becomes 0, as in src/ops.c:104 */
+struct OpRelu    { __device__ float operator()(float x) const { return x > 0.0f ? x : 0.0f; } };
+struct OpAdd     { __device__ float operator()(float x, float y) const { return x + y; } };
+struct OpMul     { __device__ float operator()(float x, float y) const { return x * y; } };
+/* mask from the forward input, src/autograd.c:323-324 */
+struct OpReluBwd { __device__ float operator()(float x, float g) const { return x > 0.0f ? g : 0.0f; } };
+struct OpReluBwdAcc { __device__ float operator()(float d, float x, float g) const { return d + (x > 0.0f ? g : 0.0f); } };
+struct OpSgd     { float lr; __device__ float operator()(float w, float g) const { return w - lr * g; } };
+
+__global__ void __launch_bounds__(TPB) fill_kernel(float *__restrict__ p, long n, float v) {
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
+}
+
+void k_fill(float *p, long n, float v) {
+    if (n <= 0) return;
+    LAUNCH(fill_kernel, grid_for(n), TPB, 0, p, n, v);
+}
+void k_copy(float *dst, const float *src, long n) {
+    if (n <= 0) return;
+    cudaMemcpyAsync(dst, src, sizeof(float) * (size_t)n, cudaMemcpyDeviceToDevice, g_tt.stream);
+}
+/* src/ops.c:26-53 (the per-element index walk of the reference is the
+ * identity on contiguous tensors, which is all it ever creates) */
+void k_add(float *o, const float *a, const float *b, long n) { run_map2(o, a, b, n, OpAdd()); }
+void k_mul(float *o, const float *a, const float *b, long n) { run_map2(o, a, b, n, OpMul()); }
+/* src/ops.c:71-82 */
+void k_addscalar(float *o, const float *a, float s, long n) { OpAddS f; f.s = s; run_map1(o, a, n, f); }
+void k_mulscalar(float *o, const float *a, float s, long n) { OpMulS f; f.s = s; run_map1(o, a, n, f); }
+/* src/autograd.c:52-54 */
+void k_accum(float *dst, const float *src, long n) { run_map2(dst, dst, src, n, OpAdd()); }
+/* src/ops.c:55-69,104-106 */
+void k_relu(float *o, const float *x, long n) { run_map1(o, x, n, OpRelu()); }
+/* src/autograd.c:318-327, optionally fused with the += of accum (:56-63) */
+void k_relu_bwd(float *dx, const float *x, const float *g, long n, int accumulate) {
+    if (accumulate) run_map3(dx, dx, x, g, n, OpReluBwdAcc());
+    else run_map2(dx, x, g, n, OpReluBwd());
+}
+void k_sgd(float *w, const float *g, float lr, long n) {
+    OpSgd f; f.lr = lr;
+    tt_trace_begin(TTB_K_OPTIM);
+    int was = g_tt.trace; g_tt.trace = 0;
+    run_map2(w, w, g, n, f);
+    g_tt.trace = was;
+    tt_trace_end(TTB_K_OPTIM, 12.0 * (double)n);
+}
+
+__global__ void __launch_bounds__(TPB) sgd_momentum_kernel(float *__restrict__ w, float *__restrict__ v,
+                                                            const float *__restrict__ g, float lr, float mu, long n) {
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float nv = mu * v[i] - lr * g[i];
+        v[i] = nv;
+        w[i] = w[i] + nv;
+    }
+}
+void k_sgd_momentum(float *w, float *v, const float *g, float lr, float mu, long n) {
+    if (n <= 0) return;
+    tt_trace_begin(TTB_K_OPTIM);
+    LAUNCH(sgd_momentum_kernel, grid_for(n), TPB, 0, w, v, g, lr, mu, n);
+    tt_trace_end(TTB_K_OPTIM, 20.0 * (double)n);
+}
+
+/* Adam exactly as tests/gate_cifar_cnn.py:92-98 writes it:
+ *   m = b1*m + (1-b1)*g ; v = b2*v + (1-b2)*g*g ; w -= lr_t * m / (sqrt(v) + eps)
+ * with lr_t = lr*sqrt(1-b2^t)/(1-b1^t) and the (1-b) factors formed on the host. */
+__global__ void __launch_bounds__(TPB) adam_kernel(float *__restrict__ w, float *__restrict__ m, float *__restrict__ v,
+                                                    const float *__restrict__ g, float lr_t, float b1, float b2,
+                                                    float omb1, float omb2, float eps, long n) {
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float gi = g[i];
+        float mi = b1 * m[i] + omb1 * gi;
+        float vi = b2 * v[i] + omb2 * (gi * gi);
+        m[i] = mi; v[i] = vi;
+        w[i] = w[i] - lr_t * mi / (sqrtf(vi) + eps);
+    }
+}
+void k_adam(float *w, float *m, float *v, const float *g, float lr_t, float b1, float b2,
+            float omb1, float omb2, float eps, long n) {
+    if (n <= 0) return;
+    tt_trace_begin(TTB_K_OPTIM);
+    LAUNCH(adam_kernel, grid_for(n), TPB, 0, w, m, v, g, lr_t, b1, b2, omb1, omb2, eps, n);
+    tt_trace_end(TTB_K_OPTIM, 28.0 * (double)n);
+}
+
+/* ---- padones and its adjoint (src/autograd.c:195-212, 348-359) ------------
+ * One thread per output element; consecutive threads write consecutive
+ * addresses, reads are contiguous runs of K. */
+__global__ void __launch_bounds__(TPB) padones_kernel(float *o, const float *__restrict__ x, int M, int K) {
+    long n = (long)M * (K + 1);
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        long m = i / (K + 1);
+        int k = (int)(i - m * (K + 1));
+        o[i] = k < K ? x[m * K + k] : 1.0f;
+    }
+}
+void k_padones(float *o, const float *x, int M, int K) {
+    tt_trace_begin(TTB_K_ELEMENTWISE);
+    LAUNCH(padones_kernel, grid_for((long)M * (K + 1)), TPB, 0, o, x, M, K);
+    tt_trace_end(TTB_K_ELEMENTWISE, 8.0 * (double)M * K);
+}
+__global__ void __launch_bounds__(TPB) slice_cols_kernel(float *o, const float *__restrict__ g,
+                                                          int M, int K, int ldg, int accumulate) {
+    long n = (long)M * K;
+    long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        long m = i / K;
+        int k = (int)(i - m * K);
+        float v = g[m * ldg + k];
+        o[i] = accumulate ? o[i] + v : v;
+    }
+}
+void k_slice_cols(float *o, const float *g, int M, int K, int ldg, int accumulate) {
+    tt_trace_begin(TTB_K_ELEMENTWISE);
+    LAUNCH(slice_cols_kernel, grid_for((long)M * K), TPB, 0, o, g, M, K, ldg, accumulate);
+    tt_trace_end(TTB_K_ELEMENTWISE, (accumulate ? 12.0 : 8.0) * (double)M * K);
+}
+
+/* ---- row reductions --------------------------------------------------------*/
+__device__ __forceinline__ float warp_max(float v) {
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { float u = __shfl_xor_sync(0xffffffffu, v, o); v = u > v ? u : v; }
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+/* Softmax over the last axis (src/ops.c:108-145): one warp per row, the row
+ * is read once per pass from L1/L2-resident lines; a row whose maximum is
+ * -Inf becomes uniform.  NaN never wins the max, as in the reference. */
+#define SM_WARPS 8
+__global__ void __launch_bounds__(SM_WARPS * 32) softmax_kernel(float *o, const float *__restrict__ x,
+                                                                  long rows, int N) {
+    int lane = threadIdx.x & 31;
+    long row = (long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
+    long rstride = (long)gridDim.x * SM_WARPS;
+    for (; row < rows; row += rstride) {
+        const float *xr = x + row * N;
+        float *orow = o + row * N;
+        float mx = -INFINITY;
+        for (int j = lane; j < N; j += 32) { float v = xr[j]; if (v > mx) mx = v; }
+        mx = warp_max(mx);
+        if (mx == -INFINITY) {
+            float u = 1.0f / (float)N;
+            for (int j = lane; j < N; j += 32) orow[j] = u;
+            continue;
+        }
+        float sum = 0.0f;
+        for (int j = lane; j < N; j += 32) sum += expf(xr[j] - mx);
+        sum = warp_sum(sum);
+        for (int j = lane; j < N; j += 32) orow[j] = expf(xr[j] - mx) / sum;
+    }
+}
+void k_softmax(float *o, const float *x, long rows, int N) {
+    if (rows <= 0) return;
+    long blocks = (rows + SM_WARPS - 1) / SM_WARPS;
+    long cap = (long)g_tt.sm_count * 8;
+    tt_trace_begin(TTB_K_SOFTMAX);
+    LAUNCH(softmax_kernel, (int)(blocks < cap ? blocks : cap), SM_WARPS * 32, 0, o, x, rows, N);
+    tt_trace_end(TTB_K_SOFTMAX, 8.0 * (double)rows * N);
+}
+
+/* dx = s * (g - sum_j g_j s_j) (src/autograd.c:329-346) */
+__global__ void __launch_bounds__(SM_WARPS * 32) softmax_bwd_kernel(float *__restrict__ dx, const float *__restrict__ s,
+                                                                      const float *__restrict__ g, long rows, int N) {
+    int lane = threadIdx.x & 31;
+    long row = (long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
+    long rstride = (long)gridDim.x * SM_WARPS;
+    for (; row < rows; row += rstride) {
+        const float *sr = s + row * N, *gr = g + row * N;
+        float dot = 0.0f;
+        for (int j = lane; j < N; j += 32) dot += gr[j] * sr[j];
+        dot = warp_sum(dot);
+        for (int j = lane; j < N; j += 32) dx[row * N + j] = sr[j] * (gr[j] - dot);
+    }
+}
+void k_softmax_bwd(float *dx, const float *s, const float *g, long rows, int N) {
+    if (rows <= 0) return;
+    long blocks = (rows + SM_WARPS - 1) / SM_WARPS;
+    long cap = (long)g_tt.sm_count * 8;
+    tt_trace_begin(TTB_K_SOFTMAX);
+    LAUNCH(softmax_bwd_kernel, (int)(blocks < cap ? blocks : cap), SM_WARPS * 32, 0, dx, s, g, rows, N);
+    tt_trace_end(TTB_K_SOFTMAX, 12.0 * (double)rows * N);
+}
+
+/* Fused softmax + cross-entropy + gradient.  Replaces softmax on the device
+ * followed by the NumPy lines of tests/gate_mnist_mlp.py:112-119:
+ *   p = softmax(z); loss_r = -log(max(p[y_r], 1e-12)); dz = (p - onehot) * scale.
+ * One pass over the logits, one write of dz, 4 bytes of loss per row. */
+__global__ void __launch_bounds__(SM_WARPS * 32) softmax_xent_kernel(const float *__restrict__ z, const float *__restrict__ labels,
+                                                                       long rows, int N, float scale,
+                                                                       float *__restrict__ dz, float *__restrict__ row_loss) {
+    int lane = threadIdx.x & 31;
+    long row = (long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
+    long rstride = (long)gridDim.x * SM_WARPS;
+    for (; row < rows; row += rstride) {
+        const float *zr = z + row * N;
+        int y = (int)labels[row];
+        float mx = -INFINITY;
+        for (int j = lane; j < N; j += 32) { float v = zr[j]; if (v > mx) mx = v; }
+        mx = warp_max(mx);
+        float py;
+        if (mx == -INFINITY) {
+            float u = 1.0f / (float)N;
+            for (int j = lane; j < N; j += 32) dz[row * N + j] = (u - (j == y ? 1.0f : 0.0f)) * scale;
+            py = u;
+        } else {
+            float sum = 0.0f;
+            for (int j = lane; j < N; j += 32) sum += expf(zr[j] - mx);
+            sum = warp_sum(sum);
+            float mine = 0.0f;
+            for (int j = lane; j < N; j += 32) {
+                float p = expf(zr[j] - mx) / sum;
+                if (j == y) mine = p;
+                dz[row * N + j] = (p - (j == y ? 1.0f : 0.0f)) * scale;
+            }
+            py = warp_sum(mine);
+        }
+        if (lane == 0) row_loss[row] = -logf(fmaxf(py, 1e-12f));
+    }
+}
+void k_softmax_xent(const float *logits, const float *labels, long rows, int N, float scale,
+                    float *dlogits, float *row_loss) {
+    if (rows <= 0) return;
+    long blocks = (rows + SM_WARPS - 1) / SM_WARPS;
+    long cap = (long)g_tt.sm_count * 8;
+    tt_trace_begin(TTB_K_SOFTMAX);
+    LAUNCH(softmax_xent_kernel, (int)(blocks < cap ? blocks : cap), SM_WARPS * 32, 0, logits, labels, rows, N, scale, dlogits, row_loss);
+    tt_trace_end(TTB_K_SOFTMAX, 8.0 * (double)rows * N);
+}
+
+/* out[0] = sum(x) / n with a fixed summation tree (one block). */
+__global__ void __launch_bounds__(1024) mean_kernel(const float *__restrict__ x, long n, float *__restrict__ out) {
+    __shared__ float part[32];
+    float s = 0.0f;
+    for (long i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        s = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.0f;
+        s = warp_sum(s);
+        if (threadIdx.x == 0) out[0] = s / (float)n;
+    }
+}
+void k_mean(const float *x, long n, float *out) {
+    tt_trace_begin(TTB_K_REDUCE);
+    LAUNCH(mean_kernel, 1, 1024, 0, x, n, out);
+    tt_trace_end(TTB_K_REDUCE, 4.0 * (double)n);
+}
+
+/* ---- column sums: out[n] (+)= sum_m g[m, n] --------------------------------
+ * The bias row of dW when padones is folded into the GEMM (the reference gets
+ * it as the last row of A^T * dC, src/autograd.c:87-103).  Two deterministic
+ * phases: each block sums a slab of rows for 128 columns into a partial row,
+ * then one pass adds the partial rows in slab order. */
+#define CS_COLS 128
+#define CS_ROWS 8
+__global__ void __launch_bounds__(CS_COLS * CS_ROWS / 4) colsum_partial_kernel(const float *__restrict__ g, int M, int N, int ldg,
+                                                                                 int rows_per_slab, float *__restrict__ part) {
+    /* 32 lanes x 4 columns wide, CS_ROWS row lanes */
+    __shared__ float4 sh[CS_ROWS][32];
+    int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    int col = blockIdx.x * CS_COLS + cx * 4;
+    int r0 = blockIdx.y * rows_per_slab;
+    int r1 = r0 + rows_per_slab < M ? r0 + rows_per_slab : M;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool vec = ((ldg & 3) == 0) && ((((uintptr_t)g) & 15u) == 0) && (col + 3 < N);
+    for (int r = r0 + ry; r < r1; r += CS_ROWS) {
+        const float *row = g + (long)r * ldg;
+        if (vec) {
+            float4 v = *(const float4 *)(row + col);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        } else {
+            if (col < N) acc.x += row[col];
+            if (col + 1 < N) acc.y += row[col + 1];
+            if (col + 2 < N) acc.z += row[col + 2];
+            if (col + 3 < N) acc.w += row[col + 3];
+        }
+    }
+    sh[ry][cx] = acc;
+    __syncthreads();
+    if (ry == 0) {
+        #pragma unroll
+        for (int k = 1; k < CS_ROWS; k++) {
+            float4 v = sh[k][cx];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        float *p = part + (long)blockIdx.y * N;
+        if (col < N) p[col] = acc.x;
+        if (col + 1 < N) p[col + 1] = acc.y;
+        if (col + 2 < N) p[col + 2] = acc.z;
+        if (col + 3 < N) p[col + 3] = acc.w;
+    }
+}
+__global__ void __launch_bounds__(TPB) colsum_final_kernel(const float *__restrict__ part, int slabs, int N,
+                                                            float *__restrict__ out, int accumulate) {
+    int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float s = 0.0f;
+    for (int k = 0; k < slabs; k++) s += part[(long)k * N + n];
+    out[n] = accumulate ? out[n] + s : s;
+}
+void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate) {
+    int slabs = (M + 63) / 64;
+    int max_slabs = (2 * g_tt.sm_count * 8) / ((N + CS_COLS - 1) / CS_COLS) + 1;
+    if (slabs > max_slabs) slabs = max_slabs;
+    if (slabs < 1) slabs = 1;
+    int rows_per_slab = (M + slabs - 1) / slabs;
+    slabs = (M + rows_per_slab - 1) / rows_per_slab;
+    float *part = (float *)tt_dev_alloc(sizeof(float) * (size_t)slabs * N);
+    if (!part) return;
+    tt_trace_begin(TTB_K_REDUCE);
+    dim3 grid((N + CS_COLS - 1) / CS_COLS, slabs);
+    LAUNCH(colsum_partial_kernel, grid, CS_COLS * CS_ROWS / 4, 0, g, M, N, ldg, rows_per_slab, part);
+    LAUNCH(colsum_final_kernel, (N + TPB - 1) / TPB, TPB, 0, part, slabs, N, out, accumulate);
+    tt_trace_end(TTB_K_REDUCE, 4.0 * (double)M * N);
+    tt_dev_free(part);
+}
+
+/* ---- transpose: o[C,R] = x[R,C]^T through a padded 32x32 tile ---------------*/
+__global__ void __launch_bounds__(256) transpose_kernel(float *o, const float *__restrict__ x, int R, int C) {
+    __shared__ float tile[32][33];
+    int bx = blockIdx.x * 32, by = blockIdx.y * 32;
+    int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int j = ty; j < 32; j += 8) {
+        int r = by + j, c = bx + tx;
+        if (r < R && c < C) tile[j][tx] = x[(long)r * C + c];
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+        int c = bx + j, r = by + tx;
+        if (r < R && c < C) o[(long)c * R + r] = tile[tx][j];
+    }
+}
+void k_transpose(float *o, const float *x, int R, int C) {
+    dim3 grid((C + 31) / 32, (R + 31) / 32);
+    tt_trace_begin(TTB_K_ELEMENTWISE);
+    LAUNCH(transpose_kernel, grid, 256, 0, o, x, R, C);
+    tt_trace_end(TTB_K_ELEMENTWISE, 8.0 * (double)R * C);
+}

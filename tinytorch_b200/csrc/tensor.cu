@@ -1,0 +1,199 @@
+/* Tensor storage: the payload lives in HBM, the public record's `data` is a
+ * lazily synchronised host mirror.
+ *
+ * Mirrors the contract of the reference's src/tensor.c (shape validation and
+ * overflow guard :10-18, zero fill :21, contiguous strides :29-32, refcount
+ * :48-61, accessors :63-75) with device memory in place of calloc. */
+#include "tt_internal.h"
+
+#include <limits.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define TT_MAX_NUMEL (1L << 40)    /* same cap as the reference (src/tensor.c:8) */
+
+/* Shape check shared by every constructor.  Returns numel, or -1. */
+static long checked_numel(const long *shape, int ndim) {
+    if (!shape || ndim <= 0 || ndim > 8) return -1;
+    long n = 1;
+    for (int i = 0; i < ndim; i++) {
+        if (shape[i] <= 0) return -1;
+        if (n > LONG_MAX / shape[i]) return -1;
+        n *= shape[i];
+    }
+    if (n > TT_MAX_NUMEL) return -1;
+    return n;
+}
+
+static TTensor *record_new(const long *shape, int ndim, long numel) {
+    TTensor *t = (TTensor *)calloc(1, sizeof(TTensor));
+    if (!t) return nullptr;
+    t->pub.shape = (long *)malloc(sizeof(long) * (size_t)ndim);
+    t->pub.strides = (long *)malloc(sizeof(long) * (size_t)ndim);
+    if (!t->pub.shape || !t->pub.strides) {
+        free(t->pub.shape); free(t->pub.strides); free(t);
+        return nullptr;
+    }
+    for (int i = 0; i < ndim; i++) t->pub.shape[i] = shape[i];
+    t->pub.strides[ndim - 1] = 1;
+    for (int i = ndim - 2; i >= 0; i--)
+        t->pub.strides[i] = t->pub.strides[i + 1] * shape[i + 1];
+    t->pub.ndim = ndim;
+    t->pub.numel = numel;
+    t->pub.refcount = 1;
+    return t;
+}
+
+static void record_free(TTensor *t) {
+    free(t->pub.data);
+    free(t->pub.shape);
+    free(t->pub.strides);
+    free(t);
+}
+
+Tensor *tt_new_uninit(const long *shape, int ndim) {
+    long numel = checked_numel(shape, ndim);
+    if (numel < 0) return nullptr;
+    TTensor *t = record_new(shape, ndim, numel);
+    if (!t) return nullptr;
+    t->dev = (float *)tt_dev_alloc(sizeof(float) * (size_t)numel);
+    if (!t->dev) { record_free(t); return nullptr; }
+    t->dev_valid = 1;
+    return &t->pub;
+}
+
+extern "C" Tensor *tt_new(const long *shape, int ndim) {
+    Tensor *t = tt_new_uninit(shape, ndim);
+    if (!t) return nullptr;
+    if (!tt_cuda_ok(cudaMemsetAsync(TT(t)->dev, 0, sizeof(float) * (size_t)t->numel, g_tt.stream),
+                    "cudaMemsetAsync")) {
+        tt_release(t);
+        return nullptr;
+    }
+    return t;
+}
+
+Tensor *tt_new_like(const Tensor *a, int zero) {
+    return zero ? tt_new(a->shape, a->ndim) : tt_new_uninit(a->shape, a->ndim);
+}
+
+extern "C" Tensor *tt_fromdata(const float *data, const long *shape, int ndim) {
+    /* The shape is judged before `data` is looked at: a hostile shape with a
+     * NULL pointer must fail here (reference: tests/test_ops.py:330-332). */
+    long numel = checked_numel(shape, ndim);
+    if (numel < 0 || !data) return nullptr;
+    Tensor *t = tt_new_uninit(shape, ndim);
+    if (!t) return nullptr;
+    /* From pageable memory this returns once the source has been staged, so
+     * the caller may reuse `data` at once; from pinned memory it is a true
+     * asynchronous copy and the caller keeps the buffer alive until the next
+     * synchronising call, as with any CUDA stream. */
+    if (!tt_cuda_ok(cudaMemcpyAsync(TT(t)->dev, data, sizeof(float) * (size_t)numel,
+                                    cudaMemcpyHostToDevice, g_tt.stream), "cudaMemcpyAsync(H2D)")) {
+        tt_release(t);
+        return nullptr;
+    }
+    return t;
+}
+
+Tensor *tt_new_lazy_padones(Tensor *src) {
+    if (!src || src->ndim != 2) return nullptr;
+    long shp[2] = {src->shape[0], src->shape[1] + 1};
+    long numel = checked_numel(shp, 2);
+    if (numel < 0) return nullptr;
+    TTensor *t = record_new(shp, 2, numel);
+    if (!t) return nullptr;
+    t->lazy_kind = TT_LAZY_PADONES;
+    t->lazy_src = TT(tt_retain(src));
+    return &t->pub;
+}
+
+extern "C" Tensor *tt_retain(Tensor *t) {
+    if (!t) return nullptr;
+    t->refcount++;
+    return t;
+}
+
+extern "C" void tt_release(Tensor *t) {
+    if (!t) return;
+    if (--t->refcount > 0) return;
+    TTensor *x = TT(t);
+    if (x->dev) tt_dev_free(x->dev);
+    if (x->lazy_src) tt_release(&x->lazy_src->pub);
+    record_free(x);
+}
+
+/* Produce a deferred payload. */
+static int materialise(TTensor *t) {
+    if (t->lazy_kind == TT_LAZY_NONE) return 1;
+    t->dev = (float *)tt_dev_alloc(sizeof(float) * (size_t)t->pub.numel);
+    if (!t->dev) return 0;
+    if (t->lazy_kind == TT_LAZY_PADONES) {
+        const float *src = tt_dev_ro(&t->lazy_src->pub);
+        if (!src) return 0;
+        k_padones(t->dev, src, (int)t->lazy_src->pub.shape[0], (int)t->lazy_src->pub.shape[1]);
+    }
+    tt_release(&t->lazy_src->pub);
+    t->lazy_src = nullptr;
+    t->lazy_kind = TT_LAZY_NONE;
+    t->dev_valid = 1;
+    return 1;
+}
+
+float *tt_dev_ro(const Tensor *ct) {
+    TTensor *t = TT(ct);
+    if (!t) return nullptr;
+    if (!materialise(t)) return nullptr;
+    if (t->host_exposed) {
+        /* The caller holds the mirror and may have written to it. */
+        if (!tt_cuda_ok(cudaMemcpyAsync(t->dev, t->pub.data, sizeof(float) * (size_t)t->pub.numel,
+                                        cudaMemcpyHostToDevice, g_tt.stream), "cudaMemcpyAsync(H2D)"))
+            return nullptr;
+        t->host_exposed = 0;
+        t->dev_valid = 1;
+    }
+    return t->dev;
+}
+
+float *tt_dev_rw(Tensor *ct) {
+    float *p = tt_dev_ro(ct);
+    if (p) TT(ct)->host_valid = 0;
+    return p;
+}
+
+extern "C" float *ttb_device_ptr(Tensor *t) { return t ? tt_dev_ro(t) : nullptr; }
+
+extern "C" float *tt_data(const Tensor *ct) {
+    TTensor *t = TT(ct);
+    if (!t) return nullptr;
+    if (!materialise(t)) return nullptr;
+    size_t bytes = sizeof(float) * (size_t)t->pub.numel;
+    if (!t->pub.data) {
+        t->pub.data = (float *)malloc(bytes);
+        if (!t->pub.data) return nullptr;
+        t->host_valid = 0;
+    }
+    if (!t->host_valid && !t->host_exposed) {
+        if (!tt_cuda_ok(cudaMemcpyAsync(t->pub.data, t->dev, bytes, cudaMemcpyDeviceToHost, g_tt.stream),
+                        "cudaMemcpyAsync(D2H)"))
+            return nullptr;
+        if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.stream), "cudaStreamSynchronize"))
+            return nullptr;
+        t->host_valid = 1;
+    }
+    t->host_exposed = 1;
+    return t->pub.data;
+}
+
+extern "C" long tt_numel(const Tensor *t) { return t ? t->numel : 0; }
+extern "C" int  tt_ndim(const Tensor *t) { return t ? t->ndim : 0; }
+
+extern "C" void tt_shape(const Tensor *t, long *out) {
+    if (!t || !out) return;
+    for (int i = 0; i < t->ndim; i++) out[i] = t->shape[i];
+}
+
+extern "C" void tt_strides(const Tensor *t, long *out) {
+    if (!t || !out) return;
+    for (int i = 0; i < t->ndim; i++) out[i] = t->strides[i];
+}

@@ -1,0 +1,137 @@
+/* Private declarations shared by the translation units of libtinytorch.so. */
+#ifndef TT_INTERNAL_H
+#define TT_INTERNAL_H
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "tensor.h"
+#include "autograd.h"
+#include "tt_b200.h"
+
+/* ---- tensor record --------------------------------------------------------
+ * The public struct comes first, so a Tensor* is also a TTensor*. */
+enum { TT_LAZY_NONE = 0, TT_LAZY_PADONES = 1 };
+
+typedef struct TTensor {
+    Tensor  pub;
+    float  *dev;           /* device payload, numel floats */
+    uint8_t dev_valid;     /* device payload is current */
+    uint8_t host_valid;    /* host mirror (pub.data) is current */
+    uint8_t host_exposed;  /* tt_data() handed the mirror out since the last upload */
+    uint8_t lazy_kind;     /* payload not produced yet: TT_LAZY_* */
+    struct TTensor *lazy_src;   /* retained source of a deferred payload */
+} TTensor;
+
+static inline TTensor *TT(const Tensor *t) { return (TTensor *)t; }
+
+/* ---- context --------------------------------------------------------------*/
+typedef struct TTContext {
+    int          ready;        /* 1 after a successful init, -1 after a failed one */
+    int          device;
+    int          sm_count;
+    cudaStream_t stream;       /* all compute */
+    cudaStream_t comm_stream;  /* NCCL all-reduce */
+    int          gemm_path;    /* 0 auto, 1 tensor core, 2 exact fp32 */
+    int          fuse_padones; /* fold padones into the adjoining GEMM */
+    int          trace;
+    long         launches;
+} TTContext;
+
+extern TTContext g_tt;
+
+int   tt_ctx_init(void);                       /* 0 ok, -1 failed (message stored) */
+void  tt_set_error(const char *fmt, ...);
+int   tt_cuda_ok(cudaError_t e, const char *what);   /* 1 ok, 0 failed (message stored) */
+void *tt_dev_alloc(size_t bytes);              /* stream-ordered, NULL on failure */
+void  tt_dev_free(void *p);
+
+/* Tensor helpers (tensor.cu). */
+Tensor *tt_new_uninit(const long *shape, int ndim);    /* device payload left unwritten */
+Tensor *tt_new_like(const Tensor *a, int zero);
+float  *tt_dev_ro(const Tensor *t);            /* device pointer for reading (uploads / materialises) */
+float  *tt_dev_rw(Tensor *t);                  /* device pointer for writing; mirror becomes stale */
+Tensor *tt_new_lazy_padones(Tensor *src);      /* [M,K] -> [M,K+1], produced on first use */
+
+/* Tracing (context.cu): bracket a launch of class `kind`. */
+void tt_trace_begin(int kind);
+void tt_trace_end(int kind, double work);
+
+/* ---- kernel launchers (all on g_tt.stream) -------------------------------- */
+/* kernels_elementwise.cu */
+void k_fill(float *p, long n, float v);
+void k_copy(float *dst, const float *src, long n);
+void k_add(float *o, const float *a, const float *b, long n);
+void k_mul(float *o, const float *a, const float *b, long n);
+void k_addscalar(float *o, const float *a, float s, long n);
+void k_mulscalar(float *o, const float *a, float s, long n);
+void k_accum(float *dst, const float *src, long n);            /* dst += src */
+void k_relu(float *o, const float *x, long n);
+void k_relu_bwd(float *dx, const float *x, const float *g, long n, int accumulate);
+void k_padones(float *o, const float *x, int M, int K);
+void k_slice_cols(float *o, const float *g, int M, int K, int ldg, int accumulate);
+void k_softmax(float *o, const float *x, long rows, int N);
+void k_softmax_bwd(float *dx, const float *s, const float *g, long rows, int N);
+void k_softmax_xent(const float *logits, const float *labels, long rows, int N,
+                    float scale, float *dlogits, float *row_loss);
+void k_mean(const float *x, long n, float *out);               /* out[0] = sum(x)/n */
+void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate);
+void k_sgd(float *w, const float *g, float lr, long n);
+void k_sgd_momentum(float *w, float *v, const float *g, float lr, float mu, long n);
+void k_adam(float *w, float *m, float *v, const float *g, float lr_t, float b1,
+            float b2, float omb1, float omb2, float eps, long n);
+void k_transpose(float *o, const float *x, int R, int C);      /* o[C,R] = x[R,C]^T */
+
+/* kernels_spatial.cu */
+void k_im2col(const float *x, int N, int C, int H, int W, int HH, int WW,
+              int ph, int pw, int sh, int sw, int Ho, int Wo, float *col);
+void k_col2im(const float *col, int N, int C, int H, int W, int HH, int WW,
+              int ph, int pw, int sh, int sw, int Ho, int Wo, float *x);
+void k_conv_unpermute_bias(const float *om, const float *bias, int N, int F, long sp, float *out);
+void k_conv_permute(const float *g, int N, int F, long sp, float *gp);
+void k_conv_bias_grad(const float *g, int N, int F, long sp, float *db);
+void k_maxpool(const float *x, long NC, int H, int W, int ph, int pw, int sh, int sw,
+               int Ho, int Wo, float *out);
+void k_maxpool_bwd(const float *x, const float *g, long NC, int H, int W, int ph, int pw,
+                   int sh, int sw, int Ho, int Wo, float *dx);
+void k_maxpool_argmax(const float *x, long NC, int H, int W, int ph, int pw, int sh, int sw,
+                      int Ho, int Wo, long long *idx);
+void k_avgpool(const float *x, long NC, int H, int W, int ph, int pw, int sh, int sw,
+               int Ho, int Wo, float *out);
+void k_avgpool_bwd(const float *g, long NC, int H, int W, int ph, int pw, int sh, int sw,
+                   int Ho, int Wo, float *dx);
+
+/* ---- GEMM -----------------------------------------------------------------
+ * C[M,N] (+)= op(A) * op(B) (+ bias[n]) with row-major storage everywhere:
+ *   ta == 0: A is [M,K] with row pitch lda;  ta == 1: A is stored [K,M]
+ *   tb == 0: B is [K,N] with row pitch ldb;  tb == 1: B is stored [N,K]
+ * accumulate != 0 adds into C.  bias (may be NULL) is one value per column.
+ * Returns 0, or -1 with the reason stored. */
+typedef struct GemmArgs {
+    int ta, tb;
+    int M, N, K;
+    const float *A; long lda;
+    const float *B; long ldb;
+    float *C; long ldc;
+    const float *bias;
+    int accumulate;
+    /* A carries a virtual last column of ones (ta == 0: logical K = stored
+     * columns + 1) or a virtual last row (ta == 1: logical M = stored rows of
+     * A^T + 1): a padones node consumed without materialising it. */
+    int a_pad_ones;
+    /* Which reference loop the exact-fp32 path reproduces bit for bit:
+     * 0 forward sgemm, 1 backward dot/axpy products, 2 naive tt_matmul. */
+    int rule;
+} GemmArgs;
+
+int tt_gemm(const GemmArgs *g);                 /* dispatch by g_tt.gemm_path */
+int gemm_simt(const GemmArgs *g);               /* gemm_simt.cu: exact fp32, k ascending */
+int gemm_tc(const GemmArgs *g);                 /* gemm_tc.cu: tcgen05 3xTF32 */
+int gemm_tc_usable(const GemmArgs *g);          /* alignment rules of the TMA path */
+
+/* dist.cu: called by the backward pass when a marked leaf's gradient is final. */
+int tt_dist_active(void);
+int tt_dist_allreduce_async(Tensor *t);
+
+#endif
