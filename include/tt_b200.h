@@ -36,6 +36,11 @@ long        ttb_launch_count(void);
 /* Device address of a tensor's payload (uploads a pending host write first). */
 float      *ttb_device_ptr(Tensor *t);
 
+/* Page-locked host memory, so that tt_fromdata / ag_backward_from copy from it
+ * with a true asynchronous DMA instead of staging through the driver. */
+void       *ttb_pinned_alloc(size_t bytes);
+void        ttb_pinned_free(void *p);
+
 /* CUDA-event timing on the library's own stream. */
 void       *ttb_event_create(void);
 void        ttb_event_record(void *ev);

@@ -78,6 +78,8 @@ EXT_ABI = {
     "ttb_sync": (CI, []),
     "ttb_launch_count": (ctypes.c_long, []),
     "ttb_device_ptr": (VP, [VP]),
+    "ttb_pinned_alloc": (VP, [ctypes.c_size_t]),
+    "ttb_pinned_free": (None, [VP]),
     "ttb_event_create": (VP, []),
     "ttb_event_record": (None, [VP]),
     "ttb_event_elapsed_ms": (ctypes.c_float, [VP, VP]),
@@ -328,6 +330,19 @@ def bind(path=None):
             if rc != 0:
                 raise RuntimeError(f"tinytorch: {name} failed{why()}")
 
+        def pinned_array(shape, dtype=np.float32):
+            """NumPy array over page-locked host memory (freed when the array dies)."""
+            nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+            ptr = lib.ttb_pinned_alloc(nbytes)
+            if not ptr:
+                raise MemoryError(f"tinytorch: ttb_pinned_alloc failed{why()}")
+            buf = (ctypes.c_char * nbytes).from_address(ptr)
+            arr = np.frombuffer(buf, dtype=dtype).reshape(shape)
+            ns._pinned.append(ptr)
+            return arr
+
+        ns._pinned = []
+        ns.pinned_array = pinned_array
         ns.matmul_nt = lambda x, y: op("ttb_matmul_nt", x.ptr, y.ptr)
         ns.matmul_tn = lambda x, y: op("ttb_matmul_tn", x.ptr, y.ptr)
         ns.relu_bwd = lambda x, g: op("ttb_relu_bwd", x.ptr, g.ptr)

@@ -105,6 +105,7 @@ extern "C" int ttb_sync(void) {
     if (tt_ctx_init() != 0) return -1;
     if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.stream), "cudaStreamSynchronize")) return -1;
     if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.comm_stream), "cudaStreamSynchronize(comm)")) return -1;
+    if (gemm_tc_poll_status()) return -1;
     return 0;
 }
 
@@ -122,6 +123,14 @@ void tt_dev_free(void *p) {
     if (!p || g_tt.ready != 1) return;
     cudaFreeAsync(p, g_tt.stream);
 }
+
+extern "C" void *ttb_pinned_alloc(size_t bytes) {
+    if (tt_ctx_init() != 0) return nullptr;
+    void *p = nullptr;
+    if (!tt_cuda_ok(cudaHostAlloc(&p, bytes ? bytes : 4, cudaHostAllocDefault), "cudaHostAlloc")) return nullptr;
+    return p;
+}
+extern "C" void ttb_pinned_free(void *p) { if (p) cudaFreeHost(p); }
 
 /* ---- events ---------------------------------------------------------------*/
 extern "C" void *ttb_event_create(void) {

@@ -79,7 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (*abort_flag) return false;
         if (clock64() - t0 > TC_WAIT_CYCLES) {
             *abort_flag = 1;
-            atomicCAS(status, 0u, code | (blockIdx.x << 8));
+            *(volatile uint32_t *)status = code | (blockIdx.x << 8);   /* plain store: the word lives in host memory */
             __threadfence_system();
             return false;
         }

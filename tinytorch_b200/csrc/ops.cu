@@ -21,8 +21,6 @@ static int same_shape(const Tensor *a, const Tensor *b) {
  * column on A is native to the exact kernel; for the tensor-core kernel it is
  * peeled off: as a bias row in the epilogue (forward), or as a column sum
  * written to the last row of C (weight gradient). */
-int gemm_tc_poll_status(void);
-
 static int tc_wanted(const GemmArgs *g) {
     if (g_tt.gemm_path == 2) return 0;
     if (g_tt.gemm_path == 1) return 1;

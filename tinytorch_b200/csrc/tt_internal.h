@@ -129,6 +129,7 @@ int tt_gemm(const GemmArgs *g);                 /* dispatch by g_tt.gemm_path */
 int gemm_simt(const GemmArgs *g);               /* gemm_simt.cu: exact fp32, k ascending */
 int gemm_tc(const GemmArgs *g);                 /* gemm_tc.cu: tcgen05 3xTF32 */
 int gemm_tc_usable(const GemmArgs *g);          /* alignment rules of the TMA path */
+int gemm_tc_poll_status(void);                  /* non-zero (reason stored) when a kernel gave up on a bounded wait */
 
 /* dist.cu: called by the backward pass when a marked leaf's gradient is final. */
 int tt_dist_active(void);
