@@ -47,7 +47,7 @@ def load_peaks():
 # ------------------------------------------------------------------ clock sampling
 class ClockSampler:
     """nvidia-smi polling in a child process for the length of the timed region."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -61,11 +61,21 @@ class ClockSampler:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+                 "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.out, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self):
+    @staticmethod
+    def _seconds(stamp):
+        """'2026/11/25 05:41:07.123' -> seconds since the epoch (local time)."""
+        import datetime
+        try:
+            return datetime.datetime.strptime(stamp.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
+    def stop(self, window=None):
+        """window = (t0, t1) in time.time() seconds: only samples inside it count."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -81,6 +91,10 @@ class ClockSampler:
                 parts = [p.strip() for p in line.split(",")]
                 if len(parts) < 9:
                     continue
+                if window is not None:
+                    ts = self._seconds(parts[0])
+                    if ts is None or ts < window[0] - 0.05 or ts > window[1] + 0.05:
+                        continue
                 try:
                     sm.append(float(parts[1])); mx.append(float(parts[2]))
                 except ValueError:
@@ -91,9 +105,7 @@ class ClockSampler:
         os.unlink(self.path)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # samples taken while the GPU is busy sit at the top of the distribution
-        busy = sorted(sm)[len(sm) // 2:]
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "samples": len(sm),
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": max(mx), "samples": len(sm),
                 "reasons": sorted(reasons)}
 
 
@@ -214,6 +226,9 @@ def run_ours(args):
     ns.status(ns.LIB.ttb_init(local), "ttb_init")
     D.connect(ns, rank, world)
     peaks, peak_kind = load_peaks()
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()                     # polls for the whole run; only the timed windows are kept
 
     x, y, ws = W.config_mlp_large(batch=GLOBAL_BATCH)
     lo, hi = D.shard_rows(GLOBAL_BATCH, rank, world)
@@ -231,9 +246,7 @@ def run_ours(args):
     for _ in range(args.warmup):
         resident_step().release()
     ns.sync(); D.barrier()
-    clocks = ClockSampler(local)
-    if rank == 0:
-        clocks.start()
+    window0 = time.time()
     ns.LIB.ttb_trace_reset(); ns.LIB.ttb_trace_enable(1)
     launches0 = ns.LIB.ttb_launch_count()
     e0, e1 = ns.LIB.ttb_event_create(), ns.LIB.ttb_event_create()
@@ -284,7 +297,7 @@ def run_ours(args):
     ns.sync(); D.barrier()
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3
     e2e_ms = D.all_max(float(max(e2e_ms, e2e_wall_ms)))
-    clock_info = clocks.stop() if rank == 0 else None
+    clock_info = clocks.stop((window0, time.time())) if rank == 0 else None
     e2e_value = GLOBAL_BATCH / (e2e_ms / args.steps * 1e-3)
 
     if rank != 0:

@@ -252,10 +252,16 @@ def _onehot(y, classes):
     return o
 
 
-def mlp_step(x, y, ws, lr=0.1, global_batch=None):
+def mlp_step(x, y, ws, lr=0.1, global_batch=None, relu_masks=None):
     """Forward + backward + SGD of x.padones().matmul(w).relu()... with the
     softmax-cross-entropy seed, as the reference executes it through its
-    autograd (tests/gate_mnist_mlp.py:104-126, src/autograd.c:308-359)."""
+    autograd (tests/gate_mnist_mlp.py:104-126, src/autograd.c:308-359).
+
+    relu_masks (one boolean array per hidden layer) replaces `pre > 0` in the
+    backward pass.  A test that compares two implementations whose forward
+    values differ in the last bits uses it to take the relu kink out of the
+    comparison: a pre-activation within rounding error of zero may land on
+    either side, and the derivative jumps there."""
     batch = x.shape[0]
     gb = global_batch or batch
     acts, pre = [], []
@@ -274,9 +280,10 @@ def mlp_step(x, y, ws, lr=0.1, global_batch=None):
         grads[i] = matmul_tn(acts[i], g)
         if i > 0:
             g = padones_bwd(matmul_nt(g, ws[i]))
-            g = relu_bwd(pre[i - 1], g)
+            gate = pre[i - 1] if relu_masks is None else np.where(relu_masks[i - 1], 1.0, -1.0).astype(np.float32)
+            g = relu_bwd(gate, g)
     new_ws = [w - np.float32(lr) * gw for w, gw in zip(ws, grads)]
-    return {"loss": loss, "logits": logits, "probs": p, "grads": grads, "weights": new_ws}
+    return {"loss": loss, "logits": logits, "probs": p, "grads": grads, "weights": new_ws, "pre": pre[:-1]}
 
 
 def cnn_step(x, y, params, global_batch=None):

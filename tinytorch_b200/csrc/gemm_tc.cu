@@ -27,7 +27,7 @@
  *               mbarriers; owns the tensor-memory allocation.
  *   warps 6-9   epilogue: tcgen05.ld the finished accumulator (one of two,
  *               so the next tile's MMAs overlap), add bias / old C, store.
- * Tile 128 x BN x 32 (BN = 256 or 128), SWIZZLE_128B everywhere.
+ * Tile 128 x BN x 32 (BN = 256 or 128), 128-byte swizzled rows everywhere.
  *
  * Every wait is bounded: a wait that exceeds its cycle budget records a code
  * in a host-visible status word, raises a CTA-wide abort flag that all other
@@ -116,19 +116,28 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 /* Shared-memory matrix descriptor (64 bit): start address, leading and stride
- * byte offsets in 16-byte units, version 1, SWIZZLE_128B.
- *   K-major tile  : rows of 128 bytes, 8-row groups 1024 bytes apart (stride
+ * byte offsets in 16-byte units, version 1, swizzle mode in the top bits.
+ *   K-major tile  : rows of 128 bytes (32 values along K), 16-byte chunks
+ *                   swizzled over 8 rows (mode 2, SWIZZLE_128B; TMA mode
+ *                   SWIZZLE_128B); 8-row groups 1024 bytes apart (stride
  *                   offset); a K step of 8 fp32 advances the start by 32 bytes.
  *   MN-major tile : built from boxes of 32 k-rows x 128 bytes (32 values along
- *                   M or N); boxes 4096 bytes apart (leading offset), 8-row
- *                   groups 1024 bytes apart; a K step advances by 1024 bytes. */
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+ *                   M or N).  For 32-bit operands the only MN-major layout the
+ *                   tensor core accepts swizzles 32-byte chunks over 4 rows
+ *                   (mode 1; TMA mode SWIZZLE_128B_ATOM_32B): 4-row groups 512
+ *                   bytes apart (stride offset), boxes 4096 bytes apart (leading
+ *                   offset); a K step of 8 rows advances the start by 1024 bytes. */
+template <int MN_MAJOR>
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
+    constexpr uint32_t lbo_bytes = MN_MAJOR ? 4096 : 16;
+    constexpr uint32_t sbo_bytes = MN_MAJOR ? 512 : 1024;
+    constexpr uint64_t mode = MN_MAJOR ? 1 : 2;
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3ffffu) >> 4);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
     d |= (uint64_t)1 << 46;            /* descriptor version for sm_100 */
-    d |= (uint64_t)2 << 61;            /* SWIZZLE_128B */
+    d |= mode << 61;
     return d;
 }
 
@@ -149,7 +158,7 @@ struct TcParams {
     uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
 };
 
-template <int A_MN, int B_MN, int BN, int STAGES>
+template <int A_MN, int B_MN, int BN, int STAGES, int SPLIT_ACC>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 4;          /* 16 KB */
@@ -159,6 +168,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)A_MN << 15) |
                                ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
     constexpr uint32_t TMEM_COLS = 2 * BN;                   /* two accumulators */
+    /* SPLIT_ACC = 0: the two accumulators alternate between tiles, so the epilogue of
+     * one tile overlaps the MMAs of the next.  SPLIT_ACC = 1 (long reductions): one
+     * holds the hi*hi products, the other the two small cross terms, and the epilogue
+     * adds them.  The tensor core truncates when it adds into an accumulator, an
+     * error that grows with the number of MMAs into a LARGE accumulator; keeping the
+     * cross terms (2^-11 of the result) apart removes two thirds of those. */
+    constexpr int NACC = SPLIT_ACC ? 1 : 2;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -245,7 +261,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 4)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t d_main = tmem_base + (uint32_t)(SPLIT_ACC ? 0 : acc * BN);
+                const uint32_t d_corr = SPLIT_ACC ? tmem_base + (uint32_t)BN : d_main;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(bar_lo + 8 * s, ph, abort_flag, p.status, 2) ||
                         !mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 2)) { ok = false; break; }
@@ -258,18 +275,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int ks = 0; ks < TC_BK / 8; ks++) {
                         const uint32_t a_off = A_MN ? ks * 1024 : ks * 32;
                         const uint32_t b_off = B_MN ? ks * 1024 : ks * 32;
-                        const uint32_t a_lbo = A_MN ? 4096 : 16, b_lbo = B_MN ? 4096 : 16;
-                        const uint64_t da_hi = make_desc(a_hi + a_off, a_lbo, 1024);
-                        const uint64_t db_hi = make_desc(b_hi + b_off, b_lbo, 1024);
+                        const uint64_t da_hi = make_desc<A_MN>(a_hi + a_off);
+                        const uint64_t db_hi = make_desc<B_MN>(b_hi + b_off);
                         const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
                         if (p.passes == 3) {
-                            const uint64_t da_lo = make_desc(a_lo + a_off, a_lbo, 1024);
-                            const uint64_t db_lo = make_desc(b_lo + b_off, b_lbo, 1024);
-                            tc_mma_tf32(d_tmem, da_lo, db_hi, IDESC, first);
-                            tc_mma_tf32(d_tmem, da_hi, db_lo, IDESC, 1u);
-                            tc_mma_tf32(d_tmem, da_hi, db_hi, IDESC, 1u);
+                            const uint64_t da_lo = make_desc<A_MN>(a_lo + a_off);
+                            const uint64_t db_lo = make_desc<B_MN>(b_lo + b_off);
+                            tc_mma_tf32(d_corr, da_lo, db_hi, IDESC, first);
+                            tc_mma_tf32(d_corr, da_hi, db_lo, IDESC, 1u);
+                            tc_mma_tf32(d_main, da_hi, db_hi, IDESC, SPLIT_ACC ? first : 1u);
                         } else {
-                            tc_mma_tf32(d_tmem, da_hi, db_hi, IDESC, first);
+                            tc_mma_tf32(d_main, da_hi, db_hi, IDESC, first);
                         }
                     }
                     tc_commit(bar_empty + 8 * s);      /* stage reusable once these MMAs have read it */
@@ -277,7 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 if (!ok) break;
                 tc_commit(bar_tfull + 8 * acc);        /* accumulator complete */
-                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
             }
         }
     } else if (warp < 6) {
@@ -321,6 +337,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                if (SPLIT_ACC && p.passes == 3) {
+                    uint32_t r2[32];
+                    tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), r2);
+                    tc_wait_ld();
+                    #pragma unroll
+                    for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                }
                 tc_wait_ld();
                 if (c0 + 32 >= BN) {
                     /* last read of this accumulator: hand it back before the stores */
@@ -357,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             }
-            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
         }
     }
 
@@ -377,6 +400,8 @@ static EncodeTiledFn g_encode = nullptr;
 static uint32_t *g_status_host = nullptr;     /* mapped pinned word the kernel reports into */
 static uint32_t *g_status_dev = nullptr;
 static int g_tc_passes = 3;
+static int g_tc_force_bn = 0;        /* TT_TC_BN: tuning aid, 0 = choose by tile count */
+static int g_tc_split_k = 1024;      /* reductions longer than this use the split accumulators */
 
 static int tc_setup(void) {
     if (g_encode && g_status_host) return 0;
@@ -394,6 +419,10 @@ static int tc_setup(void) {
     if (!tt_cuda_ok(cudaHostGetDevicePointer((void **)&g_status_dev, g_status_host, 0), "cudaHostGetDevicePointer")) return -1;
     const char *e = getenv("TT_TC_PASSES");
     if (e && atoi(e) == 1) g_tc_passes = 1;
+    e = getenv("TT_TC_BN");
+    if (e && *e) g_tc_force_bn = atoi(e);
+    e = getenv("TT_TC_SPLIT_K");
+    if (e && *e) g_tc_split_k = atoi(e);
     return 0;
 }
 
@@ -410,13 +439,15 @@ int gemm_tc_poll_status(void) {
 }
 
 /* inner = contiguous extent, outer = number of rows, pitch in floats */
-static int encode_map(CUtensorMap *map, const float *base, long inner, long outer, long pitch, int box_inner, int box_outer) {
+static int encode_map(CUtensorMap *map, const float *base, long inner, long outer, long pitch, int box_inner, int box_outer,
+                      int mn_major) {
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
     cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { tt_set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return -1; }
     return 0;
@@ -431,11 +462,11 @@ int gemm_tc_usable(const GemmArgs *g) {
     return 1;
 }
 
-template <int A_MN, int B_MN, int BN, int STAGES>
+template <int A_MN, int B_MN, int BN, int STAGES, int SPLIT_ACC>
 static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb) {
     constexpr size_t smem = (size_t)STAGES * 2 * (TC_BM * TC_BK * 4 + BN * TC_BK * 4) + 1024 + 8 * (3 * STAGES + 4) + 16;
     static bool configured = false;
-    auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES>;
+    auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES, SPLIT_ACC>;
     if (!configured) {
         if (!tt_cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                         "cudaFuncSetAttribute(smem)")) return -1;
@@ -453,13 +484,13 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     return tt_cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch") ? 0 : -1;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int SPLIT_ACC>
 static int launch_tc_major(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb) {
     const int a_mn = g->ta ? 1 : 0, b_mn = g->tb ? 0 : 1;
-    if (!a_mn && !b_mn) return launch_tc<0, 0, BN, STAGES>(g, ma, mb);
-    if (!a_mn && b_mn)  return launch_tc<0, 1, BN, STAGES>(g, ma, mb);
-    if (a_mn && !b_mn)  return launch_tc<1, 0, BN, STAGES>(g, ma, mb);
-    return launch_tc<1, 1, BN, STAGES>(g, ma, mb);
+    if (!a_mn && !b_mn) return launch_tc<0, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb);
+    if (!a_mn && b_mn)  return launch_tc<0, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb);
+    if (a_mn && !b_mn)  return launch_tc<1, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb);
+    return launch_tc<1, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb);
 }
 
 int gemm_tc(const GemmArgs *g) {
@@ -467,12 +498,15 @@ int gemm_tc(const GemmArgs *g) {
     if (tc_setup() != 0) return -1;
     /* 128x256 tiles unless that leaves most SMs idle */
     const long tiles256 = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + 255) / 256);
-    const int bn = (tiles256 * 10 < (long)g_tt.sm_count * 7 || g->N <= 128) ? 128 : 256;
+    int bn = (tiles256 * 10 < (long)g_tt.sm_count * 7 || g->N <= 128) ? 128 : 256;
+    if (g_tc_force_bn == 128 || g_tc_force_bn == 256) bn = g_tc_force_bn;
     CUtensorMap ma, mb;
-    if (g->ta) { if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, 32)) return -1; }
-    else       { if (encode_map(&ma, g->A, g->K, g->M, g->lda, TC_BK, TC_BM)) return -1; }
-    if (g->tb) { if (encode_map(&mb, g->B, g->K, g->N, g->ldb, TC_BK, bn)) return -1; }
-    else       { if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, 32)) return -1; }
-    if (bn == 256) return launch_tc_major<256, 2>(g, ma, mb);
-    return launch_tc_major<128, 3>(g, ma, mb);
+    if (g->ta) { if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, 32, 1)) return -1; }
+    else       { if (encode_map(&ma, g->A, g->K, g->M, g->lda, TC_BK, TC_BM, 0)) return -1; }
+    if (g->tb) { if (encode_map(&mb, g->B, g->K, g->N, g->ldb, TC_BK, bn, 0)) return -1; }
+    else       { if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, 32, 1)) return -1; }
+    /* long reductions keep the cross terms in their own accumulator (see the kernel) */
+    const bool split_acc = g->K > g_tc_split_k;
+    if (bn == 256) return split_acc ? launch_tc_major<256, 2, 1>(g, ma, mb) : launch_tc_major<256, 2, 0>(g, ma, mb);
+    return split_acc ? launch_tc_major<128, 3, 1>(g, ma, mb) : launch_tc_major<128, 3, 0>(g, ma, mb);
 }

@@ -108,9 +108,10 @@ def onehot(y, classes):
 
 
 # ----------------------------------------------------------------- gate-script style
-def mlp_step_reference_style(ns, x, y, ws, lr=0.1, global_batch=None):
+def mlp_step_reference_style(ns, x, y, ws, lr=0.1, global_batch=None, return_pre=False):
     """One forward + backward + SGD step exactly as tests/gate_mnist_mlp.py:104-126
-    runs it (plain SGD instead of momentum).  Returns loss, gradients, new weights."""
+    runs it (plain SGD instead of momentum).  Returns loss, gradients, new weights;
+    with return_pre also the pre-activations of the hidden layers."""
     Node = ns.Node
     batch = x.shape[0]
     gb = global_batch or batch
@@ -122,9 +123,11 @@ def mlp_step_reference_style(ns, x, y, ws, lr=0.1, global_batch=None):
 
     wn = [keep(Node.leaf(w, True)) for w in ws]
     h = keep(Node.leaf(x, False))
+    pre_nodes = []
     for i, w in enumerate(wn):
         h = keep(keep(h.padones()).matmul(w))
         if i + 1 < len(wn):
+            pre_nodes.append(h)
             h = keep(h.relu())
     logits = h
     probs = keep(logits.softmax())
@@ -133,10 +136,11 @@ def mlp_step_reference_style(ns, x, y, ws, lr=0.1, global_batch=None):
     logits.backward((p - onehot(y, p.shape[1])) / gb)
     grads = [w.grad() for w in wn]
     logits_v = logits.value()
+    pre = [n.value() for n in pre_nodes] if return_pre else None
     for n in nodes:
         n.release()
     new_ws = [w - np.float32(lr) * g for w, g in zip(ws, grads)]
-    return {"loss": loss, "logits": logits_v, "probs": p, "grads": grads, "weights": new_ws}
+    return {"loss": loss, "logits": logits_v, "probs": p, "grads": grads, "weights": new_ws, "pre": pre}
 
 
 def cnn_forward(ns, keep, xn, pn):
