@@ -180,13 +180,13 @@ def workload_config(n_gpus):
 
 
 # ------------------------------------------------------------------ our arm
-def gemm_block(ns, peaks):
+def gemm_block(ns, peaks, cases=((1024, 20), (4096, 5))):
     """Forward + backward GEMM throughput (C = A*B, dA = dC*B^T, dB = A^T*dC) on
-    square 1024 and 4096 problems, L2 flushed between repetitions."""
+    square problems, L2 flushed between repetitions."""
     out = []
     tf32_peak = peaks["bf16_tflops"] / 2.0
     flush = ns.Tensor.zeros((64 * 1024 * 1024,))          # 256 MB > 126 MB of L2
-    for n, reps in ((1024, 20), (4096, 5)):
+    for n, reps in cases:
         a, b, dc = W.config_gemm(n, 1 if n == 1024 else 4)
         an, bn = ns.Node.leaf(a, True), ns.Node.leaf(b, True)
         dct = ns.Tensor.from_np(dc)
@@ -350,6 +350,26 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
 
 
+def run_gemm(args):
+    """Isolated forward + backward GEMM (BASELINE.json configs[1] and the square
+    sizes of configs[4]); also the small case the ncu captures run."""
+    import tinytorch_b200
+    ns = tinytorch_b200.default()
+    if ns.device_count() < 1:
+        raise SystemExit("bench.py: no CUDA device visible; this library has no CPU path")
+    peaks, peak_kind = load_peaks()
+    res = gemm_block(ns, peaks, cases=((args.gemm_n, max(args.steps, 1)),))[0]
+    line = {"metric": "gemm_fwd_bwd_tflops", "value": res["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": res["ms"], "higher_is_better": True,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"isolated GEMM forward + backward, square {args.gemm_n}", "l2": "flushed between repetitions"},
+            "roofline": {"bound": "tensor", "achieved": res["tflops"], "peak": peaks["bf16_tflops"] / 2.0, "unit": "TFLOP/s",
+                         "frac": res["frac_of_tf32_peak"], "traffic": None,
+                         "peak_source": f"{peak_kind} bf16_tflops / 2 (burst: kernel timed alone)"},
+            "gpu_launches": int(ns.LIB.ttb_launch_count())}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -360,11 +380,15 @@ def main():
                     help="samples per CPU step of the reference arm / CPU baseline (a slice of the global batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
+    ap.add_argument("--workload", choices=["mlp", "gemm"], default="mlp")
+    ap.add_argument("--gemm-n", type=int, default=4096)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "gemm":
+        run_gemm(args)
     else:
         run_ours(args)
 
