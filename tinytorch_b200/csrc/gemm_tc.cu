@@ -12,20 +12,21 @@
  * Precision.  kind::tf32 reads 32-bit words and uses the top 19 bits.  Each
  * fp32 operand x is therefore split as hi = x with the low 13 mantissa bits
  * cleared (what the instruction sees when it is handed x itself) and
- * lo = x - hi (exact in fp32, rounded to tf32), and every K step issues
+ * lo = x - hi (exact in fp32; the instruction keeps its top 19 bits), and every K step issues
  *   D += A_lo*B_hi;  D += A_hi*B_lo;  D += A_hi*B_hi
  * into one fp32 accumulator.  The dropped A_lo*B_lo term is below 2^-20
  * relative, so products carry about 21 bits, which is what "fp32-grade"
  * means for this kernel.
  *
- * Structure of one CTA (persistent, one per SM, 320 threads):
+ * Structure of one CTA (persistent, one per SM, 448 threads):
  *   warp 0      TMA producer: cp.async.bulk.tensor loads (no multicast) of
- *               the raw A and B tiles of a K block into a ring of stages.
- *   warps 2-5   split: read the raw tiles from shared memory, write the lo
+ *               the raw A and B tiles of a K block into a ring of stages, and
+ *               L2 prefetches a few K blocks ahead so that those loads hit L2.
+ *   warps 2-9   split: read the raw tiles from shared memory, write the lo
  *               tiles next to them at the same (swizzled) offsets.
  *   warp 1      one thread issues the tcgen05.mma triples and commits to
  *               mbarriers; owns the tensor-memory allocation.
- *   warps 6-9   epilogue: tcgen05.ld the finished accumulator (one of two,
+ *   warps 10-13 epilogue: tcgen05.ld the finished accumulator (one of two,
  *               so the next tile's MMAs overlap), add bias / old C, store.
  * Tile 128 x BN x 32 (BN = 256 or 128), 128-byte swizzled rows everywhere.
  *
@@ -40,8 +41,9 @@
 
 #define TC_BM 128
 #define TC_BK 32                 /* 32 fp32 = one 128-byte swizzle span */
-#define TC_THREADS 320
-#define TC_SPLIT_THREADS 128
+#define TC_THREADS 448
+#define TC_SPLIT_THREADS 256
+#define TC_PREFETCH 6            /* K blocks the producer asks L2 for ahead of its loads */
 #define TC_EPI_THREADS 128
 #define TC_WAIT_CYCLES (1ll << 30)
 
@@ -89,6 +91,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+/* Ask L2 for a tile without taking shared memory: the loads that follow hit L2. */
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -141,12 +148,12 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
     return d;
 }
 
-/* lo part of the 3xTF32 split: x minus its 19-bit truncation, rounded to tf32. */
+/* lo part of the 3xTF32 split: x minus its 19-bit truncation (exact in fp32; the
+ * instruction reads its top 19 bits). */
 __device__ __forceinline__ float split_lo(float x) {
     float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
     float lo = x - hi;
-    if (fabsf(x) == INFINITY) lo = 0.0f;       /* keep Inf an Inf instead of Inf - Inf */
-    return __uint_as_float((__float_as_uint(lo) + 0x1000u) & 0xffffe000u);
+    return fabsf(x) == INFINITY ? 0.0f : lo;   /* keep Inf an Inf instead of Inf - Inf */
 }
 
 struct TcParams {
@@ -223,28 +230,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            /* this CTA's work as one sequence of (tile, K block) items */
+            const long my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const long items = my_tiles * num_kb;
+            auto prefetch = [&](long it) {
+                const int t = blockIdx.x + (int)(it / num_kb) * gridDim.x, k0 = (int)(it % num_kb) * TC_BK;
                 const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
-                for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
-                    const uint32_t st = smem_base + s * STAGE_BYTES;
-                    const uint32_t full = bar_full + 8 * s;
-                    mbar_expect_tx(full, HI_BYTES);
-                    const int k0 = kb * TC_BK;
-                    if (A_MN) {
-                        #pragma unroll
-                        for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * 4096, &map_a, full, m0 + 32 * b, k0);
-                    } else {
-                        tma_load_2d(st, &map_a, full, k0, m0);
-                    }
-                    if (B_MN) {
-                        #pragma unroll
-                        for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * 4096, &map_b, full, n0 + 32 * b, k0);
-                    } else {
-                        tma_load_2d(st + A_BYTES, &map_b, full, k0, n0);
-                    }
-                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                if (A_MN) {
+                    #pragma unroll
+                    for (int b = 0; b < TC_BM / 32; b++) tma_prefetch_2d(&map_a, m0 + 32 * b, k0);
+                } else {
+                    tma_prefetch_2d(&map_a, k0, m0);
                 }
+                if (B_MN) {
+                    #pragma unroll
+                    for (int b = 0; b < BN / 32; b++) tma_prefetch_2d(&map_b, n0 + 32 * b, k0);
+                } else {
+                    tma_prefetch_2d(&map_b, k0, n0);
+                }
+            };
+            for (long it = STAGES; it < TC_PREFETCH && it < items; it++) prefetch(it);
+            for (long it = 0; it < items; it++) {
+                if (it + TC_PREFETCH < items) prefetch(it + TC_PREFETCH);
+                const int t = blockIdx.x + (int)(it / num_kb) * gridDim.x, k0 = (int)(it % num_kb) * TC_BK;
+                const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
+                if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
+                const uint32_t st = smem_base + s * STAGE_BYTES;
+                const uint32_t full = bar_full + 8 * s;
+                mbar_expect_tx(full, HI_BYTES);
+                if (A_MN) {
+                    #pragma unroll
+                    for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * 4096, &map_a, full, m0 + 32 * b, k0);
+                } else {
+                    tma_load_2d(st, &map_a, full, k0, m0);
+                }
+                if (B_MN) {
+                    #pragma unroll
+                    for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * 4096, &map_b, full, n0 + 32 * b, k0);
+                } else {
+                    tma_load_2d(st + A_BYTES, &map_b, full, k0, n0);
+                }
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             if (!ok) {
                 /* give loads already in flight time to land before the CTA exits */
@@ -296,7 +322,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 2 + TC_SPLIT_THREADS / 32) {
         /* ---------------- split warps: lo = x - trunc19(x) ---------------- */
         const int st_tid = threadIdx.x - 64;
         int s = 0; uint32_t ph = 0;
