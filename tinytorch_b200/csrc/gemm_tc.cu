@@ -92,6 +92,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, int x, int y, int z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(z) : "memory");
+}
 /* Ask L2 for a tile without taking shared memory: the loads that follow hit L2. */
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
@@ -162,6 +171,7 @@ struct TcParams {
     const float *bias;
     int accumulate;
     int passes;              /* 3 = full split, 1 = hi*hi only (bring-up aid) */
+    int a_3d, b_3d;          /* MN-major operand described by a rank-3 map: one TMA per tile instead of one per 32 columns */
     uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
 };
 
@@ -236,13 +246,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             auto prefetch = [&](long it) {
                 const int t = blockIdx.x + (int)(it / num_kb) * gridDim.x, k0 = (int)(it % num_kb) * TC_BK;
                 const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
-                if (A_MN) {
+                if (A_MN && p.a_3d) {
+                    tma_prefetch_3d(&map_a, 0, k0, m0 / 32);
+                } else if (A_MN) {
                     #pragma unroll
                     for (int b = 0; b < TC_BM / 32; b++) tma_prefetch_2d(&map_a, m0 + 32 * b, k0);
                 } else {
                     tma_prefetch_2d(&map_a, k0, m0);
                 }
-                if (B_MN) {
+                if (B_MN && p.b_3d) {
+                    tma_prefetch_3d(&map_b, 0, k0, n0 / 32);
+                } else if (B_MN) {
                     #pragma unroll
                     for (int b = 0; b < BN / 32; b++) tma_prefetch_2d(&map_b, n0 + 32 * b, k0);
                 } else {
@@ -258,13 +272,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t st = smem_base + s * STAGE_BYTES;
                 const uint32_t full = bar_full + 8 * s;
                 mbar_expect_tx(full, HI_BYTES);
-                if (A_MN) {
+                if (A_MN && p.a_3d) {
+                    tma_load_3d(st, &map_a, full, 0, k0, m0 / 32);
+                } else if (A_MN) {
                     #pragma unroll
                     for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * 4096, &map_a, full, m0 + 32 * b, k0);
                 } else {
                     tma_load_2d(st, &map_a, full, k0, m0);
                 }
-                if (B_MN) {
+                if (B_MN && p.b_3d) {
+                    tma_load_3d(st + A_BYTES, &map_b, full, 0, k0, n0 / 32);
+                } else if (B_MN) {
                     #pragma unroll
                     for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * 4096, &map_b, full, n0 + 32 * b, k0);
                 } else {
@@ -427,6 +445,7 @@ static uint32_t *g_status_host = nullptr;     /* mapped pinned word the kernel r
 static uint32_t *g_status_dev = nullptr;
 static int g_tc_passes = 3;
 static int g_tc_force_bn = 0;        /* TT_TC_BN: tuning aid, 0 = choose by tile count */
+static int g_tc_mn3d = 1;            /* TT_TC_MN3D=0: tuning aid, one TMA per 32 columns for MN-major tiles */
 static int g_tc_split_k = 1024;      /* reductions longer than this use the split accumulators */
 
 static int tc_setup(void) {
@@ -445,6 +464,8 @@ static int tc_setup(void) {
     if (!tt_cuda_ok(cudaHostGetDevicePointer((void **)&g_status_dev, g_status_host, 0), "cudaHostGetDevicePointer")) return -1;
     const char *e = getenv("TT_TC_PASSES");
     if (e && atoi(e) == 1) g_tc_passes = 1;
+    e = getenv("TT_TC_MN3D");
+    if (e && *e) g_tc_mn3d = atoi(e);
     e = getenv("TT_TC_BN");
     if (e && *e) g_tc_force_bn = atoi(e);
     e = getenv("TT_TC_SPLIT_K");
@@ -479,6 +500,21 @@ static int encode_map(CUtensorMap *map, const float *base, long inner, long oute
     return 0;
 }
 
+/* MN-major operand stored [K rows][MN] with MN a multiple of 32, seen as a rank-3 tensor
+ * {32 values, K rows, MN/32 column groups} with strides {4, pitch*4, 128} bytes.  A box
+ * {32, 32, groups} then lands in shared memory group after group, 32 k-rows of 128 bytes
+ * each -- the layout the kernel's MN-major descriptors expect -- with ONE copy per tile. */
+static int encode_map_mn3d(CUtensorMap *map, const float *base, long mn, long k, long pitch, int groups) {
+    cuuint64_t dims[3] = {32, (cuuint64_t)k, (cuuint64_t)(mn / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)pitch * sizeof(float), 128};
+    cuuint32_t box[3] = {32, 32, (cuuint32_t)groups};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -1;
+}
+
 int gemm_tc_usable(const GemmArgs *g) {
     if (g->a_pad_ones) return 0;
     if (g->M <= 0 || g->N <= 0 || g->K <= 0) return 0;
@@ -489,7 +525,7 @@ int gemm_tc_usable(const GemmArgs *g) {
 }
 
 template <int A_MN, int B_MN, int BN, int STAGES, int SPLIT_ACC>
-static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb) {
+static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
     constexpr size_t smem = (size_t)STAGES * 2 * (TC_BM * TC_BK * 4 + BN * TC_BK * 4) + 1024 + 8 * (3 * STAGES + 4) + 16;
     static bool configured = false;
     auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES, SPLIT_ACC>;
@@ -501,6 +537,7 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     TcParams p;
     p.M = g->M; p.N = g->N; p.K = g->K; p.C = g->C; p.ldc = g->ldc; p.bias = g->bias;
     p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev;
+    p.a_3d = a_3d; p.b_3d = b_3d;
     int tiles = ((g->M + TC_BM - 1) / TC_BM) * ((g->N + BN - 1) / BN);
     int grid = tiles < g_tt.sm_count ? tiles : g_tt.sm_count;
     tt_trace_begin(TTB_K_GEMM_TC);
@@ -511,12 +548,12 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
 }
 
 template <int BN, int STAGES, int SPLIT_ACC>
-static int launch_tc_major(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb) {
+static int launch_tc_major(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
     const int a_mn = g->ta ? 1 : 0, b_mn = g->tb ? 0 : 1;
-    if (!a_mn && !b_mn) return launch_tc<0, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb);
-    if (!a_mn && b_mn)  return launch_tc<0, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb);
-    if (a_mn && !b_mn)  return launch_tc<1, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb);
-    return launch_tc<1, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb);
+    if (!a_mn && !b_mn) return launch_tc<0, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
+    if (!a_mn && b_mn)  return launch_tc<0, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
+    if (a_mn && !b_mn)  return launch_tc<1, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
+    return launch_tc<1, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
 }
 
 int gemm_tc(const GemmArgs *g) {
@@ -527,12 +564,17 @@ int gemm_tc(const GemmArgs *g) {
     int bn = (tiles256 * 10 < (long)g_tt.sm_count * 7 || g->N <= 128) ? 128 : 256;
     if (g_tc_force_bn == 128 || g_tc_force_bn == 256) bn = g_tc_force_bn;
     CUtensorMap ma, mb;
-    if (g->ta) { if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, 32, 1)) return -1; }
-    else       { if (encode_map(&ma, g->A, g->K, g->M, g->lda, TC_BK, TC_BM, 0)) return -1; }
-    if (g->tb) { if (encode_map(&mb, g->B, g->K, g->N, g->ldb, TC_BK, bn, 0)) return -1; }
-    else       { if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, 32, 1)) return -1; }
+    int a_3d = 0, b_3d = 0;
+    if (g->ta) {
+        if (g_tc_mn3d && g->M % 32 == 0 && encode_map_mn3d(&ma, g->A, g->M, g->K, g->lda, TC_BM / 32) == 0) a_3d = 1;
+        else if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, 32, 1)) return -1;
+    } else if (encode_map(&ma, g->A, g->K, g->M, g->lda, TC_BK, TC_BM, 0)) return -1;
+    if (g->tb) {
+        if (encode_map(&mb, g->B, g->K, g->N, g->ldb, TC_BK, bn, 0)) return -1;
+    } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, bn / 32) == 0) b_3d = 1;
+    else if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, 32, 1)) return -1;
     /* long reductions keep the cross terms in their own accumulator (see the kernel) */
     const bool split_acc = g->K > g_tc_split_k;
-    if (bn == 256) return split_acc ? launch_tc_major<256, 2, 1>(g, ma, mb) : launch_tc_major<256, 2, 0>(g, ma, mb);
-    return split_acc ? launch_tc_major<128, 3, 1>(g, ma, mb) : launch_tc_major<128, 3, 0>(g, ma, mb);
+    if (bn == 256) return split_acc ? launch_tc_major<256, 2, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 2, 0>(g, ma, mb, a_3d, b_3d);
+    return split_acc ? launch_tc_major<128, 3, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 3, 0>(g, ma, mb, a_3d, b_3d);
 }
