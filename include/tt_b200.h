@@ -72,6 +72,10 @@ Tensor *ttb_matmul_tn(const Tensor *x, const Tensor *y);
  * softmax: dx = s * (g - sum(g*s)) per row      (src/autograd.c:329-346) */
 Tensor *ttb_relu_bwd(const Tensor *x, const Tensor *g);
 Tensor *ttb_softmax_bwd(const Tensor *s, const Tensor *g);
+/* Column sums of a 2-D tensor: out[n] = sum over rows of g[m, n].  This is the
+ * bias row of a weight gradient, which the reference obtains as the last row of
+ * A^T * dC with A carrying a ones column (src/autograd.c:87-103, 195-212). */
+Tensor *ttb_colsum(const Tensor *g);
 /* Batched im2col and its adjoint (src/ops_spatial.c:37-69,
  * src/autograd.c:406-434).  x is [N,C,H,W]; col is [C*kh*kw, N*Hout*Wout]. */
 Tensor *ttb_im2col(const Tensor *x, int kh, int kw, int stride_h, int stride_w,

@@ -363,6 +363,17 @@ def test_full_size_gemm_checksum_of_checksums(tt, n):
         assert abs(c[i, j] - a64[i] @ b64[:, j]) <= 1e-4 * np.abs(c).max()
 
 
+@pytest.mark.parametrize("shape", [(1, 1), (7, 5), (128, 10), (130, 1000), (1000, 257), (8192, 4096), (3, 5000)])
+def test_column_sums(tt, shape):
+    """Bias row of a weight gradient: tree sum here, sequential in the reference."""
+    g = np.random.default_rng(shape[0]).standard_normal(shape).astype(np.float32)
+    gt = T(tt, g)
+    out = tt.colsum(gt)
+    want = g.astype(np.float64).sum(0)
+    assert np.allclose(out.to_np(), want, rtol=2e-5, atol=1e-5 * np.sqrt(shape[0]))
+    gt.release(); out.release()
+
+
 def test_optimizer_steps_match_numpy(tt):
     rng = np.random.default_rng(12)
     w = rng.standard_normal((257, 33)).astype(np.float32)

@@ -92,6 +92,7 @@ EXT_ABI = {
     "ttb_matmul_nt": (VP, [VP, VP]),
     "ttb_matmul_tn": (VP, [VP, VP]),
     "ttb_relu_bwd": (VP, [VP, VP]),
+    "ttb_colsum": (VP, [VP]),
     "ttb_softmax_bwd": (VP, [VP, VP]),
     "ttb_im2col": (VP, [VP, CI, CI, CI, CI, CI, CI]),
     "ttb_col2im": (VP, [VP, CI, CI, CI, CI, CI, CI, CI, CI, CI, CI]),
@@ -346,6 +347,7 @@ def bind(path=None):
         ns.matmul_nt = lambda x, y: op("ttb_matmul_nt", x.ptr, y.ptr)
         ns.matmul_tn = lambda x, y: op("ttb_matmul_tn", x.ptr, y.ptr)
         ns.relu_bwd = lambda x, g: op("ttb_relu_bwd", x.ptr, g.ptr)
+        ns.colsum = lambda g: op("ttb_colsum", g.ptr)
         ns.softmax_bwd = lambda s, g: op("ttb_softmax_bwd", s.ptr, g.ptr)
         ns.im2col = lambda x, kh, kw, sh, sw, ph, pw: op("ttb_im2col", x.ptr, kh, kw, sh, sw, ph, pw)
         ns.col2im = lambda col, n, c, h, w, kh, kw, sh, sw, ph, pw: op(

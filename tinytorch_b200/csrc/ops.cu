@@ -111,6 +111,17 @@ extern "C" Tensor *ttb_relu_bwd(const Tensor *x, const Tensor *g) {
     return out;
 }
 
+extern "C" Tensor *ttb_colsum(const Tensor *g) {
+    if (!g || g->ndim != 2 || g->shape[0] > 0x7fffffffL || g->shape[1] > 0x7fffffffL) return nullptr;
+    const float *pg = tt_dev_ro(g);
+    if (!pg) return nullptr;
+    long shp[1] = {g->shape[1]};
+    Tensor *out = tt_new_uninit(shp, 1);
+    if (!out) return nullptr;
+    k_colsum(pg, (int)g->shape[0], (int)g->shape[1], (int)g->shape[1], TT(out)->dev, 0);
+    return out;
+}
+
 /* ---- softmax (src/ops.c:108-145, src/autograd.c:329-346) -------------------*/
 extern "C" Tensor *tt_softmax(const Tensor *a) {
     if (!a || a->ndim < 1) return nullptr;
