@@ -76,6 +76,19 @@ Tensor *ttb_softmax_bwd(const Tensor *s, const Tensor *g);
  * bias row of a weight gradient, which the reference obtains as the last row of
  * A^T * dC with A carrying a ones column (src/autograd.c:87-103, 195-212). */
 Tensor *ttb_colsum(const Tensor *g);
+/* The same column sums for a caller that may not allocate device memory at the
+ * moment of the call: an application whose own arena owns all of the GPU's
+ * memory, a loop that cannot afford an allocator call, code running while a
+ * stream is being recorded.  The partial sums go to a 2 MiB array built into the
+ * library instead of pool memory, so the call itself performs no allocation.
+ * g_dev is [rows, cols] with row pitch ldg (floats), out_dev holds cols floats;
+ * both are device addresses (ttb_device_ptr) and the work is queued on the
+ * library's stream.  accumulate != 0 adds into out_dev.  At most 16384 columns;
+ * more is refused with -1 and a message.  The first call on a device looks the
+ * array's address up; make it before recording that device's stream.  All calls
+ * share the array: do not let two of them overlap on the GPU.  There is no
+ * counterpart in the reference, which is host code over malloc. */
+int     ttb_colsum_static(const float *g_dev, int rows, int cols, long ldg, float *out_dev, int accumulate);
 /* Batched im2col and its adjoint (src/ops_spatial.c:37-69,
  * src/autograd.c:406-434).  x is [N,C,H,W]; col is [C*kh*kw, N*Hout*Wout]. */
 Tensor *ttb_im2col(const Tensor *x, int kh, int kw, int stride_h, int stride_w,

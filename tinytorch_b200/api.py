@@ -93,6 +93,7 @@ EXT_ABI = {
     "ttb_matmul_tn": (VP, [VP, VP]),
     "ttb_relu_bwd": (VP, [VP, VP]),
     "ttb_colsum": (VP, [VP]),
+    "ttb_colsum_static": (CI, [VP, CI, CI, ctypes.c_long, VP, CI]),
     "ttb_softmax_bwd": (VP, [VP, VP]),
     "ttb_im2col": (VP, [VP, CI, CI, CI, CI, CI, CI]),
     "ttb_col2im": (VP, [VP, CI, CI, CI, CI, CI, CI, CI, CI, CI, CI]),

@@ -447,6 +447,60 @@ void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate)
     tt_dev_free(part);
 }
 
+/* ---- column sums for callers that must not allocate ----------------------------
+ * Some hosts of this library cannot reach the device allocator when they need a
+ * bias gradient: a process that handed every byte of device memory to its own
+ * arena at start-up and forbids any other allocation afterwards, a latency-bound
+ * loop in which an allocator call is not acceptable, or code that runs while a
+ * stream is being recorded, where asking the driver for memory is an error.  For
+ * them the partial sums live in a fixed array inside the library image instead
+ * of in pool memory.  Every GPU that loads the library carries the array
+ * (TTB_COLSUM_STATIC_SLABS x TTB_COLSUM_STATIC_MAX_COLS floats = 2 MiB) until
+ * the process exits.
+ *
+ * The array's name is only a stand-in on the host; what a kernel can use is the
+ * address cudaGetSymbolAddress returns for it on the current device.  That
+ * lookup is done here, once per device, on the first call made with that device
+ * current -- so make the first call on a device before recording a stream.
+ * All calls share the one array.  Each call overwrites every partial it later
+ * reads, so nothing has to be cleared; but two calls that run on the GPU at the
+ * same time (different streams, or different host threads) would trample each
+ * other's partials.  Calls made through the library's single stream are safe. */
+#define TTB_COLSUM_STATIC_SLABS 32
+#define TTB_COLSUM_STATIC_MAX_COLS 16384
+static __device__ __align__(256) float g_colsum_static[TTB_COLSUM_STATIC_SLABS * TTB_COLSUM_STATIC_MAX_COLS];
+static float *g_colsum_static_addr[64];        /* device address of the array, per device ordinal */
+
+extern "C" int ttb_colsum_static(const float *g_dev, int rows, int cols, long ldg, float *out_dev, int accumulate) {
+    if (!g_dev || !out_dev || rows <= 0 || cols <= 0 || ldg < cols || ldg > 0x7fffffffL) {
+        tt_set_error("ttb_colsum_static: bad arguments");
+        return -1;
+    }
+    if (cols > TTB_COLSUM_STATIC_MAX_COLS) {
+        tt_set_error("ttb_colsum_static: %d columns exceed the built-in scratch (%d); use ttb_colsum",
+                     cols, TTB_COLSUM_STATIC_MAX_COLS);
+        return -1;
+    }
+    if (tt_ctx_init() != 0) return -1;
+    int dev = -1;
+    if (!tt_cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return -1;
+    if (dev < 0 || dev >= 64) { tt_set_error("ttb_colsum_static: device ordinal %d not supported", dev); return -1; }
+    if (!g_colsum_static_addr[dev]) {
+        float *addr = nullptr;
+        if (!tt_cuda_ok(cudaGetSymbolAddress((void **)&addr, g_colsum_static), "cudaGetSymbolAddress") || !addr) return -1;
+        g_colsum_static_addr[dev] = addr;
+    }
+    float *part = g_colsum_static_addr[dev];
+    int slabs = (rows + 63) / 64;
+    if (slabs > TTB_COLSUM_STATIC_SLABS) slabs = TTB_COLSUM_STATIC_SLABS;
+    int rows_per_slab = (rows + slabs - 1) / slabs;
+    slabs = (rows + rows_per_slab - 1) / rows_per_slab;
+    dim3 grid((cols + CS_COLS - 1) / CS_COLS, slabs);
+    LAUNCH(colsum_partial_kernel, grid, CS_COLS * CS_ROWS / 4, 0, g_dev, rows, cols, (int)ldg, rows_per_slab, part);
+    LAUNCH(colsum_final_kernel, (cols + TPB - 1) / TPB, TPB, 0, part, slabs, cols, out_dev, accumulate);
+    return tt_cuda_ok(cudaGetLastError(), "ttb_colsum_static launch") ? 0 : -1;
+}
+
 /* ---- transpose: o[C,R] = x[R,C]^T through a padded 32x32 tile ---------------*/
 __global__ void __launch_bounds__(256) transpose_kernel(float *o, const float *__restrict__ x, int R, int C) {
     __shared__ float tile[32][33];
