@@ -370,6 +370,136 @@ def run_gemm(args):
     print(json.dumps(line), flush=True)
 
 
+def _time_op(ns, fn, reps=10, warm=3):
+    """Median CUDA-event time (ms) of fn(), which enqueues work and returns tensors to release."""
+    times = []
+    for r in range(reps + warm):
+        e0, e1 = ns.LIB.ttb_event_create(), ns.LIB.ttb_event_create()
+        ns.LIB.ttb_event_record(e0)
+        outs = fn()
+        ns.LIB.ttb_event_record(e1)
+        ms = ns.LIB.ttb_event_elapsed_ms(e0, e1)
+        ns.LIB.ttb_event_destroy(e0); ns.LIB.ttb_event_destroy(e1)
+        for t in outs:
+            t.release()
+        if r >= warm:
+            times.append(ms)
+    return statistics.median(times)
+
+
+def run_kernels(args):
+    """HBM-bound kernels of the path, one by one, at the sizes the CNN and the large
+    MLP use them (inputs larger than L2 where the configuration allows): achieved
+    algorithmic GB/s against the measured copy bandwidth, and the oracle on one
+    host thread beside each."""
+    import tinytorch_b200
+    from oracle import oracle as O
+    ns = tinytorch_b200.default()
+    if ns.device_count() < 1:
+        raise SystemExit("bench.py: no CUDA device visible; this library has no CPU path")
+    peaks, peak_kind = load_peaks()
+    hbm = peaks["hbm_gbs"]
+    rng = np.random.default_rng(0)
+    T = ns.Tensor.from_np
+    rows = []
+
+    def add(name, nbytes, fn, cpu_fn=None, cpu_scale=1.0):
+        ms = _time_op(ns, fn)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        row = {"kernel": name, "bytes": int(nbytes), "ms": ms, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm}
+        if cpu_fn is not None and not args.no_cpu_baseline:
+            t0 = time.perf_counter(); cpu_fn(); dt = time.perf_counter() - t0
+            row["cpu_oracle_ms"] = dt * 1e3 * cpu_scale
+        rows.append(row)
+
+    # large MLP activations: [8192, 4096] = 134 MB
+    x = rng.standard_normal((8192, 4096)).astype(np.float32); g = rng.standard_normal((8192, 4096)).astype(np.float32)
+    xt, gt = T(x), T(g)
+    small = slice(0, 512)
+    add("relu [8192,4096]", 8 * x.size, lambda: [ns.Tensor(ns.LIB.tt_relu(xt.ptr))], lambda: O.relu(x[small]), 16)
+    add("relu_bwd [8192,4096]", 12 * x.size, lambda: [ns.relu_bwd(xt, gt)], lambda: O.relu_bwd(x[small], g[small]), 16)
+    add("colsum [8192,4096]", 4 * x.size, lambda: [ns.colsum(gt)])
+    w = T(x[:4097]); gw = T(g[:4097])
+    add("sgd [4097,4096]", 12 * 4097 * 4096, lambda: (ns.sgd_step(w, gw, 0.1), [])[1])
+    for t in (xt, gt, w, gw):
+        t.release()
+    # the spatial and softmax tensors of the configurations are 30-80 MB and take 10-20 us, less than the
+    # host needs to enqueue the next launch; they are scaled up eightfold (same row and plane shapes, more
+    # rows / images) so that the timing sees the kernel and not the launch path
+    z = rng.standard_normal((65536, 1000)).astype(np.float32); y = rng.integers(0, 1000, size=65536).astype(np.float32)
+    zt, yt = T(z), T(y)
+    add("softmax_xent [65536,1000]", 8 * z.size, lambda: list(ns.softmax_xent(zt, yt, 1.0 / 8192)), lambda: O.softmax(z[small]), 128)
+    add("softmax [65536,1000]", 8 * z.size, lambda: [ns.Tensor(ns.LIB.tt_softmax(zt.ptr))])
+    zt.release(); yt.release()
+    # CNN tensors, 2048 images
+    B = 2048
+    a1 = rng.standard_normal((B, 32, 32, 32)).astype(np.float32)              # conv1 output
+    a1t = T(a1)
+    g1 = rng.standard_normal((B, 32, 16, 16)).astype(np.float32); g1t = T(g1)
+    add(f"maxpool 2x2 [{B},32,32,32]", 4 * (a1.size + g1.size), lambda: [ns.Tensor(ns.LIB.tt_maxpool2d(a1t.ptr, 2, 2, 2, 2))],
+        lambda: O.maxpool(a1[:16], 2, 2, 2, 2), B / 16)
+    add(f"maxpool_bwd 2x2 [{B},32,32,32]", 4 * (2 * a1.size + g1.size), lambda: [ns.maxpool_bwd(a1t, g1t, 2, 2, 2, 2)],
+        lambda: O.maxpool_bwd(a1[:16], g1[:16], 2, 2, 2, 2), B / 16)
+    a1t.release(); del a1
+    p1 = g1; p1t = g1t                                                          # conv2 input has the same shape
+    col_bytes = 4 * (288 * B * 256)
+    add(f"im2col 3x3 p1 [{B},32,16,16]", col_bytes + 4 * p1.size, lambda: [ns.im2col(p1t, 3, 3, 1, 1, 1, 1)],
+        lambda: O.im2col(p1[:16], 3, 3, 1, 1, 1, 1), B / 16)
+    colt = ns.im2col(p1t, 3, 3, 1, 1, 1, 1)
+    add(f"col2im 3x3 p1 [{B},32,16,16]", col_bytes + 4 * p1.size, lambda: [ns.col2im(colt, B, 32, 16, 16, 3, 3, 1, 1, 1, 1)])
+    for t in (g1t, colt):
+        t.release()
+    line = {"metric": "hbm_bound_kernels_gbs", "value": statistics.median([r["gbs"] for r in rows]), "unit": "GB/s",
+            "n_gpus": 1, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "memory-bound kernels of the training path, one by one", "l2": "operands 130-700 MB"},
+            "peak": {"hbm_gbs": hbm, "source": peak_kind}, "kernels": rows, "gpu_launches": int(ns.LIB.ttb_launch_count())}
+    print(json.dumps(line), flush=True)
+
+
+def run_cnn(args):
+    """BASELINE.json configs[2]: the CNN forward + backward at batch 256, driven the
+    way the reference's CIFAR gate drives it (leaves from NumPy each step, softmax to
+    NumPy, seed from NumPy, gradients back to NumPy), against the reference library
+    doing the same on the host cores."""
+    import tinytorch_b200
+    ns = tinytorch_b200.default()
+    if ns.device_count() < 1:
+        raise SystemExit("bench.py: no CUDA device visible; this library has no CPU path")
+    x, y, p = W.config_cnn(256)
+    for _ in range(3):
+        W.cnn_step_reference_style(ns, x, y, p)
+    ns.sync()
+    l0 = ns.LIB.ttb_launch_count()
+    times = []
+    for _ in range(max(args.steps, 1)):
+        t0 = time.perf_counter()
+        r = W.cnn_step_reference_style(ns, x, y, p)
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    line = {"metric": "cnn_fwd_bwd_samples_per_sec", "value": 256 / sec, "unit": "samples/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": sec * 1e3, "higher_is_better": True, "dtype": "f32",
+            "data": "synthetic", "loss": r["loss"],
+            "config": {"workload": "CNN conv3x3(3->32) relu pool conv3x3(32->64) relu pool fc4096->256 relu fc256->10, "
+                                   "batch 256, host arrays in and gradients out every step (BASELINE.json configs[2])"},
+            "e2e": {"value": 256 / sec, "unit": "samples/s",
+                    "h2d_bytes_per_step": int(x.nbytes + sum(v.nbytes for v in p.values()) + 256 * 10 * 4),
+                    "d2h_bytes_per_step": int(sum(v.nbytes for v in p.values()) + 2 * 256 * 10 * 4)},
+            "gpu_launches": int(ns.LIB.ttb_launch_count() - l0)}
+    if not args.no_cpu_baseline:
+        from oracle import oracle as O
+        ref = O.load_ref()
+        xs, ys = x[:64], y[:64]
+        t0 = time.perf_counter()
+        if ref is not None:
+            W.cnn_step_reference_style(ref, xs, ys, p); kind = "reference"
+        else:
+            O.cnn_step(xs, ys, p); kind = "port"
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 64 / dt, "unit": "samples/s", "cores": host_threads(), "kind": kind,
+                                "sample": "one step on 64 of the 256 samples"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -380,7 +510,7 @@ def main():
                     help="samples per CPU step of the reference arm / CPU baseline (a slice of the global batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
-    ap.add_argument("--workload", choices=["mlp", "gemm"], default="mlp")
+    ap.add_argument("--workload", choices=["mlp", "gemm", "kernels", "cnn"], default="mlp")
     ap.add_argument("--gemm-n", type=int, default=4096)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
@@ -389,6 +519,10 @@ def main():
         run_reference(args)
     elif args.workload == "gemm":
         run_gemm(args)
+    elif args.workload == "kernels":
+        run_kernels(args)
+    elif args.workload == "cnn":
+        run_cnn(args)
     else:
         run_ours(args)
 

@@ -286,9 +286,16 @@ def mlp_step(x, y, ws, lr=0.1, global_batch=None, relu_masks=None):
     return {"loss": loss, "logits": logits, "probs": p, "grads": grads, "weights": new_ws, "pre": pre[:-1]}
 
 
-def cnn_step(x, y, params, global_batch=None):
+def cnn_step(x, y, params, global_batch=None, forward=None):
     """Forward + backward of the benchmark CNN (graph of tests/gate_cifar_cnn.py:101-111
-    with two conv blocks) through the oracle's operators."""
+    with two conv blocks) through the oracle's operators.
+
+    forward (dict with z1, z2, z3, logits) evaluates the BACKWARD pass at somebody
+    else's forward values instead of the oracle's own.  relu and max-pool are not
+    differentiable where a pre-activation is zero or two window entries tie; two
+    implementations whose forward values differ in the last bits take different
+    branches there.  A test first shows that the forward values agree, then
+    compares gradients at the same point."""
     batch = x.shape[0]
     gb = global_batch or batch
     z1 = conv2d(x, params["w1"], params["b1"], 1, 1, 1, 1)
@@ -305,6 +312,14 @@ def cnn_step(x, y, params, global_batch=None):
     logits = sgemm(f2, params["fc2"])
     p = softmax(logits)
     loss = float(-np.log(np.maximum(p[np.arange(batch), y], 1e-12)).mean())
+    own = {"z1": z1, "z2": z2, "z3": z3}
+    if forward is not None:
+        z1, z2, z3 = _f(forward["z1"]), _f(forward["z2"]), _f(forward["z3"])
+        a1 = relu(z1); p1 = maxpool(a1, 2, 2, 2, 2)
+        a2 = relu(z2); p2 = maxpool(a2, 2, 2, 2, 2)
+        f1 = padones(p2.reshape(batch, -1))
+        f2 = padones(relu(z3))
+        p = softmax(_f(forward["logits"]))
     g = ((p - _onehot(y, p.shape[1])) / gb).astype(np.float32)
     grads = {}
     grads["fc2"] = matmul_tn(f2, g)
@@ -317,7 +332,7 @@ def cnn_step(x, y, params, global_batch=None):
     g, _ = maxpool_bwd(a1, g, 2, 2, 2, 2)
     g = relu_bwd(z1, g)
     _, grads["w1"], grads["b1"] = conv2d_bwd(x, params["w1"], g, 1, 1, 1, 1, need_dx=False)
-    return {"loss": loss, "logits": logits, "grads": grads}
+    return {"loss": loss, "logits": logits, "grads": grads, "pre": own}
 
 
 def gemm_fwd_bwd(a, b, dc):

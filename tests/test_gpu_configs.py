@@ -72,7 +72,6 @@ def test_config2_gemm_1024_forward_backward(tt, golden_steps):
 
 def _check_cnn(got, want, tol):
     assert abs(got["loss"] - want["loss"]) < 1e-4
-    assert rel_err(got["logits"], want["logits"]) <= tol
     for k in want["grads"]:
         assert rel_err(got["grads"][k], want["grads"][k]) <= tol, k
 
@@ -80,41 +79,62 @@ def _check_cnn(got, want, tol):
 def test_config3_cnn_batch16_against_fixture_and_oracle(tt, orc, golden_steps):
     g = golden_steps
     x, y, p = W.config_cnn(16)
-    got = W.cnn_step_reference_style(tt, x, y, p)
-    want = orc.cnn_step(x, y, p)
+    got = W.cnn_step_reference_style(tt, x, y, p, return_pre=True)
+    plain = orc.cnn_step(x, y, p)
+    assert rel_err(got["logits"], plain["logits"]) <= TOL
+    want = orc.cnn_step(x, y, p, forward=dict(got["pre"], logits=got["logits"]))   # gradients at our forward point
     _check_cnn(got, want, TOL)
     assert abs(got["loss"] - float(g["cfg3_loss"])) < 1e-4
     assert rel_err(got["logits"], g["cfg3_logits"]) <= TOL
-    for k in ("w1", "b1", "b2", "fc2"):
-        assert rel_err(got["grads"][k], g[f"cfg3_g_{k}"]) <= TOL, k
-    for k in ("w2", "fc1"):
-        assert rel_err(got["grads"][k].reshape(-1)[g[f"cfg3_g_{k}_idx"]], g[f"cfg3_g_{k}_val"]) <= TOL, k
+    # the fixture is the reference's own output: on the exact path the forward pass reproduces it bit
+    # for bit (conv, pool and fc chains), and the gradients differ only through expf in the seed
     with exact_path(tt):
         ex = W.cnn_step_reference_style(tt, x, y, p)
-    assert np.array_equal(ex["logits"], g["cfg3_logits"])            # conv, pool and fc chains reproduce the reference
+    assert np.array_equal(ex["logits"], g["cfg3_logits"])
+    for k in ("w1", "b1", "b2", "fc2"):
+        assert rel_err(ex["grads"][k], g[f"cfg3_g_{k}"]) <= 2e-5, k
+    for k in ("w2", "fc1"):
+        assert rel_err(ex["grads"][k].reshape(-1)[g[f"cfg3_g_{k}_idx"]], g[f"cfg3_g_{k}_val"]) <= 2e-5, k
 
 
 def test_config3_cnn_full_batch_256(tt, orc):
-    """Full-size CNN step against the oracle.  The conv weight gradients reduce
-    over 262,144 / 65,536 terms, beyond the 8192 the 1e-4 bound is stated for:
-    there both implementations are judged against float64 and ours must not be
-    worse than the reference's own arithmetic."""
+    """Full-size CNN step against the oracle.  With 8.4 million relu inputs and 2 million
+    pooling windows some sit on a kink (a pre-activation within rounding error of zero, two
+    window entries within rounding error of each other), where the two implementations may
+    take different branches.  So: the forward passes must agree; every sign disagreement must
+    sit at the kink; and the gradients are compared with the oracle differentiating at OUR
+    forward values.  The conv weight gradients reduce over 262,144 / 65,536 terms, beyond the
+    8192 the 1e-4 bound is stated for, and are held to 5e-4."""
     x, y, p = W.config_cnn(256)
-    got = W.cnn_step_reference_style(tt, x, y, p)
-    want = orc.cnn_step(x, y, p)
-    assert abs(got["loss"] - want["loss"]) < 1e-4
-    assert rel_err(got["logits"], want["logits"]) <= TOL
+    got = W.cnn_step_reference_style(tt, x, y, p, return_pre=True)
+    plain = orc.cnn_step(x, y, p)
+    assert abs(got["loss"] - plain["loss"]) < 1e-4
+    assert rel_err(got["logits"], plain["logits"]) <= TOL
+    for k in ("z1", "z2", "z3"):
+        zg, zo = got["pre"][k], plain["pre"][k]
+        assert rel_err(zg, zo) <= TOL, k
+        flipped = (zg > 0) != (zo > 0)
+        assert flipped.mean() < 1e-4, k
+        assert np.all(np.abs(zo[flipped]) <= TOL * np.abs(zo).max()), k
+    want = orc.cnn_step(x, y, p, forward=dict(got["pre"], logits=got["logits"]))
     for k in ("fc1", "fc2", "b1", "b2"):
         assert rel_err(got["grads"][k], want["grads"][k]) <= TOL, k
     for k in ("w1", "w2"):
         assert rel_err(got["grads"][k], want["grads"][k]) <= 5e-4, k
+    with exact_path(tt):                   # on the exact path there are no kinks to argue about
+        ex = W.cnn_step_reference_style(tt, x, y, p)
+    assert np.array_equal(ex["logits"], plain["logits"])
+    for k in ("fc1", "fc2", "w2"):
+        assert rel_err(ex["grads"][k], plain["grads"][k]) <= 2e-5, k
 
 
 def test_config4_large_mlp_scaled(tt, orc, golden_steps):
     """Real layer widths, batch 64 (fixture) and batch 128 (tensor-core path, live oracle)."""
     g = golden_steps
     x, y, ws = W.config_mlp_large(batch=64)
-    got = W.mlp_step_reference_style(tt, x, y, ws, lr=0.1, global_batch=64)
+    with exact_path(tt):                   # fixture = the reference's own output: compare on the exact path
+        got = W.mlp_step_reference_style(tt, x, y, ws, lr=0.1, global_batch=64)
+    assert np.array_equal(got["logits"].reshape(-1)[g["cfg4_logits_idx"]], g["cfg4_logits_val"])
     assert abs(got["loss"] - float(g["cfg4_loss"])) < 1e-4
     for i, gw in enumerate(got["grads"]):
         err = np.abs(gw.reshape(-1)[g[f"cfg4_g{i}_idx"]].astype(np.float64) - g[f"cfg4_g{i}_val"]).max() / float(g[f"cfg4_g{i}_abs_max"])

@@ -172,6 +172,11 @@ struct TcParams {
     int accumulate;
     int passes;              /* 3 = full split, 1 = hi*hi only (bring-up aid) */
     int a_3d, b_3d;          /* MN-major operand described by a rank-3 map: one TMA per tile instead of one per 32 columns */
+    /* Split-K: the reduction is cut into `splits` slices of kb_per_split K blocks; slice s of a tile
+     * writes its partial product to partial + s*M*N (row pitch N) and a second kernel adds the slices
+     * in order.  splits == 1: the epilogue writes C itself. */
+    int splits, kb_per_split;
+    float *partial;
     uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
 };
 
@@ -211,6 +216,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + TC_BK - 1) / TC_BK;
+    const int num_items = num_tiles * p.splits;          /* work items: (K slice, tile) */
+    /* item -> first row, first column, K-block range, slice */
+    auto decode = [&](int it, int &m0, int &n0, int &kb0, int &kb1, int &split) {
+        split = it / num_tiles;
+        const int t = it - split * num_tiles;
+        m0 = (t % tiles_m) * TC_BM; n0 = (t / tiles_m) * BN;
+        kb0 = split * p.kb_per_split;
+        kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -240,12 +254,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool ok = true;
-            /* this CTA's work as one sequence of (tile, K block) items */
-            const long my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-            const long items = my_tiles * num_kb;
-            auto prefetch = [&](long it) {
-                const int t = blockIdx.x + (int)(it / num_kb) * gridDim.x, k0 = (int)(it % num_kb) * TC_BK;
-                const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
+            auto prefetch = [&](int m0, int n0, int kb) {
+                const int k0 = kb * TC_BK;
                 if (A_MN && p.a_3d) {
                     tma_prefetch_3d(&map_a, 0, k0, m0 / 32);
                 } else if (A_MN) {
@@ -263,32 +273,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tma_prefetch_2d(&map_b, k0, n0);
                 }
             };
-            for (long it = STAGES; it < TC_PREFETCH && it < items; it++) prefetch(it);
-            for (long it = 0; it < items; it++) {
-                if (it + TC_PREFETCH < items) prefetch(it + TC_PREFETCH);
-                const int t = blockIdx.x + (int)(it / num_kb) * gridDim.x, k0 = (int)(it % num_kb) * TC_BK;
-                const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
-                if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
-                const uint32_t st = smem_base + s * STAGE_BYTES;
-                const uint32_t full = bar_full + 8 * s;
-                mbar_expect_tx(full, HI_BYTES);
-                if (A_MN && p.a_3d) {
-                    tma_load_3d(st, &map_a, full, 0, k0, m0 / 32);
-                } else if (A_MN) {
-                    #pragma unroll
-                    for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * 4096, &map_a, full, m0 + 32 * b, k0);
-                } else {
-                    tma_load_2d(st, &map_a, full, k0, m0);
+            for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
+                int m0, n0, kb0, kb1, split;
+                decode(it, m0, n0, kb0, kb1, split);
+                if (it == (int)blockIdx.x)
+                    for (int kb = kb0 + STAGES; kb < kb0 + TC_PREFETCH && kb < kb1; kb++) prefetch(m0, n0, kb);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    /* keep L2 TC_PREFETCH K blocks ahead, running on into this CTA's next item */
+                    const int pk = kb + TC_PREFETCH;
+                    if (pk < kb1) {
+                        prefetch(m0, n0, pk);
+                    } else if (it + (int)gridDim.x < num_items) {
+                        int m2, n2, kb2, kb3, s2;
+                        decode(it + gridDim.x, m2, n2, kb2, kb3, s2);
+                        if (kb2 + (pk - kb1) < kb3) prefetch(m2, n2, kb2 + (pk - kb1));
+                    }
+                    if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
+                    const uint32_t st = smem_base + s * STAGE_BYTES;
+                    const uint32_t full = bar_full + 8 * s;
+                    const int k0 = kb * TC_BK;
+                    mbar_expect_tx(full, HI_BYTES);
+                    if (A_MN && p.a_3d) {
+                        tma_load_3d(st, &map_a, full, 0, k0, m0 / 32);
+                    } else if (A_MN) {
+                        #pragma unroll
+                        for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * 4096, &map_a, full, m0 + 32 * b, k0);
+                    } else {
+                        tma_load_2d(st, &map_a, full, k0, m0);
+                    }
+                    if (B_MN && p.b_3d) {
+                        tma_load_3d(st + A_BYTES, &map_b, full, 0, k0, n0 / 32);
+                    } else if (B_MN) {
+                        #pragma unroll
+                        for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * 4096, &map_b, full, n0 + 32 * b, k0);
+                    } else {
+                        tma_load_2d(st + A_BYTES, &map_b, full, k0, n0);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
-                if (B_MN && p.b_3d) {
-                    tma_load_3d(st + A_BYTES, &map_b, full, 0, k0, n0 / 32);
-                } else if (B_MN) {
-                    #pragma unroll
-                    for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * 4096, &map_b, full, n0 + 32 * b, k0);
-                } else {
-                    tma_load_2d(st + A_BYTES, &map_b, full, k0, n0);
-                }
-                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             if (!ok) {
                 /* give loads already in flight time to land before the CTA exits */
@@ -302,12 +324,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int s = 0; uint32_t ph = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
+                int m0, n0, kb0, kb1, split;
+                decode(it, m0, n0, kb0, kb1, split);
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 4)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_main = tmem_base + (uint32_t)(SPLIT_ACC ? 0 : acc * BN);
                 const uint32_t d_corr = SPLIT_ACC ? tmem_base + (uint32_t)BN : d_main;
-                for (int kb = 0; kb < num_kb; kb++) {
+                for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(bar_lo + 8 * s, ph, abort_flag, p.status, 2) ||
                         !mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 2)) { ok = false; break; }
                     tc_fence_after();
@@ -321,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const uint32_t b_off = B_MN ? ks * 1024 : ks * 32;
                         const uint64_t da_hi = make_desc<A_MN>(a_hi + a_off);
                         const uint64_t db_hi = make_desc<B_MN>(b_hi + b_off);
-                        const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
+                        const uint32_t first = (kb > kb0 || ks > 0) ? 1u : 0u;
                         if (p.passes == 3) {
                             const uint64_t da_lo = make_desc<A_MN>(a_lo + a_off);
                             const uint64_t db_lo = make_desc<B_MN>(b_lo + b_off);
@@ -345,8 +369,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int st_tid = threadIdx.x - 64;
         int s = 0; uint32_t ph = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-            for (int kb = 0; kb < num_kb; kb++) {
+        for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
+            int m0, n0, kb0, kb1, split;
+            decode(it, m0, n0, kb0, kb1, split);
+            for (int kb = kb0; kb < kb1; kb++) {
                 const bool got = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 1);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }     /* keep the warp together */
                 if (p.passes == 3) {
@@ -369,14 +395,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int q = warp & 3;                       /* tensor-memory lane quarter this warp may read */
         int acc = 0; uint32_t acc_ph = 0;
         bool ok = true;
-        const bool vec_ok = ((p.ldc & 3) == 0) && ((((uintptr_t)p.C) & 15u) == 0);
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-            const int m0 = (t % tiles_m) * TC_BM, n0 = (t / tiles_m) * BN;
+        const bool sliced = p.splits > 1;
+        const long ldc = sliced ? (long)p.N : p.ldc;
+        const float *bias = sliced ? nullptr : p.bias;
+        const int accumulate = sliced ? 0 : p.accumulate;
+        for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
+            int m0, n0, kb0, kb1, split;
+            decode(it, m0, n0, kb0, kb1, split);
+            float *cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
+            const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0);
             const bool got = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5);
             if (!__all_sync(0xffffffffu, got)) { ok = false; break; }         /* tcgen05.ld needs the whole warp */
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
-            float *crow = p.C + (long)row * p.ldc;
+            float *crow = cbase + (long)row * ldc;
             #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -401,11 +433,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (int j = 0; j < 32; j += 4) {
                             float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
                                                    __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            if (p.bias) {
-                                v.x += p.bias[gc + j]; v.y += p.bias[gc + j + 1];
-                                v.z += p.bias[gc + j + 2]; v.w += p.bias[gc + j + 3];
+                            if (bias) {
+                                v.x += bias[gc + j]; v.y += bias[gc + j + 1];
+                                v.z += bias[gc + j + 2]; v.w += bias[gc + j + 3];
                             }
-                            if (p.accumulate) {
+                            if (accumulate) {
                                 float4 o = *(const float4 *)(crow + gc + j);
                                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                             }
@@ -416,8 +448,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (int j = 0; j < 32; j++) {
                             if (gc + j < p.N) {
                                 float v = __uint_as_float(r[j]);
-                                if (p.bias) v += p.bias[gc + j];
-                                if (p.accumulate) v += crow[gc + j];
+                                if (bias) v += bias[gc + j];
+                                if (accumulate) v += crow[gc + j];
                                 crow[gc + j] = v;
                             }
                         }
@@ -436,6 +468,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+/* Second phase of split-K: C[m,n] (+)= bias[n] + sum over slices, slices added in order. */
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, int splits, int M, int N,
+                                                             float *__restrict__ C, long ldc, const float *__restrict__ bias,
+                                                             int accumulate) {
+    const long total = (long)M * N;
+    const long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int m = (int)(i / N), n = (int)(i - (long)m * N);
+        float s = 0.0f;
+        for (int k = 0; k < splits; k++) s += partial[(long)k * total + i];
+        if (bias) s += bias[n];
+        float *c = C + (long)m * ldc + n;
+        *c = accumulate ? *c + s : s;
+    }
+}
+
 /* ---- host side ----------------------------------------------------------------*/
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -445,6 +493,7 @@ static uint32_t *g_status_host = nullptr;     /* mapped pinned word the kernel r
 static uint32_t *g_status_dev = nullptr;
 static int g_tc_passes = 3;
 static int g_tc_force_bn = 0;        /* TT_TC_BN: tuning aid, 0 = choose by tile count */
+static int g_tc_splitk = 1;          /* TT_TC_SPLITK=0: tuning aid, never cut the reduction across CTAs */
 static int g_tc_mn3d = 1;            /* TT_TC_MN3D=0: tuning aid, one TMA per 32 columns for MN-major tiles */
 static int g_tc_split_k = 1024;      /* reductions longer than this use the split accumulators */
 
@@ -464,6 +513,8 @@ static int tc_setup(void) {
     if (!tt_cuda_ok(cudaHostGetDevicePointer((void **)&g_status_dev, g_status_host, 0), "cudaHostGetDevicePointer")) return -1;
     const char *e = getenv("TT_TC_PASSES");
     if (e && atoi(e) == 1) g_tc_passes = 1;
+    e = getenv("TT_TC_SPLITK");
+    if (e && *e) g_tc_splitk = atoi(e);
     e = getenv("TT_TC_MN3D");
     if (e && *e) g_tc_mn3d = atoi(e);
     e = getenv("TT_TC_BN");
@@ -524,6 +575,9 @@ int gemm_tc_usable(const GemmArgs *g) {
     return 1;
 }
 
+/* Split-K plan of the launch being prepared (host side, single caller thread). */
+static struct { int splits, kb_per_split; float *partial; } g_plan = {1, 0, nullptr};
+
 template <int A_MN, int B_MN, int BN, int STAGES, int SPLIT_ACC>
 static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
     constexpr size_t smem = (size_t)STAGES * 2 * (TC_BM * TC_BK * 4 + BN * TC_BK * 4) + 1024 + 8 * (3 * STAGES + 4) + 16;
@@ -538,11 +592,19 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     p.M = g->M; p.N = g->N; p.K = g->K; p.C = g->C; p.ldc = g->ldc; p.bias = g->bias;
     p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev;
     p.a_3d = a_3d; p.b_3d = b_3d;
-    int tiles = ((g->M + TC_BM - 1) / TC_BM) * ((g->N + BN - 1) / BN);
+    p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
+    int tiles = ((g->M + TC_BM - 1) / TC_BM) * ((g->N + BN - 1) / BN) * p.splits;
     int grid = tiles < g_tt.sm_count ? tiles : g_tt.sm_count;
     tt_trace_begin(TTB_K_GEMM_TC);
     kern<<<grid, TC_THREADS, smem, g_tt.stream>>>(ma, mb, p);
     g_tt.launches++;
+    if (p.splits > 1) {
+        long total = (long)g->M * g->N;
+        long blocks = (total + 255) / 256, cap = (long)g_tt.sm_count * 8;
+        splitk_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
+            p.partial, p.splits, g->M, g->N, g->C, g->ldc, g->bias, g->accumulate);
+        g_tt.launches++;
+    }
     tt_trace_end(TTB_K_GEMM_TC, 2.0 * (double)g->M * g->N * g->K);
     return tt_cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch") ? 0 : -1;
 }
@@ -573,8 +635,30 @@ int gemm_tc(const GemmArgs *g) {
         if (encode_map(&mb, g->B, g->K, g->N, g->ldb, TC_BK, bn, 0)) return -1;
     } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, bn / 32) == 0) b_3d = 1;
     else if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, 32, 1)) return -1;
+    /* Split-K when the tiles alone leave most SMs idle and the reduction is long enough to cut:
+     * slices of at least four K blocks, as many as fill the machine, partials in pool scratch. */
+    const int num_kb = (g->K + TC_BK - 1) / TC_BK;
+    const long tiles = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + bn - 1) / bn);
+    g_plan.splits = 1; g_plan.kb_per_split = num_kb; g_plan.partial = nullptr;
+    if (g_tc_splitk && tiles * 2 <= g_tt.sm_count && num_kb >= 8) {
+        long want = g_tt.sm_count / tiles;
+        if (want > num_kb / 4) want = num_kb / 4;
+        const long max_by_mem = (256l << 20) / ((long)g->M * g->N * 4 + 1);
+        if (want > max_by_mem) want = max_by_mem;
+        if (want >= 2) {
+            const int per = (int)((num_kb + want - 1) / want);
+            const int splits = (num_kb + per - 1) / per;
+            float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * g->M * g->N);
+            if (!scratch) return -1;
+            g_plan.splits = splits; g_plan.kb_per_split = per; g_plan.partial = scratch;
+        }
+    }
     /* long reductions keep the cross terms in their own accumulator (see the kernel) */
-    const bool split_acc = g->K > g_tc_split_k;
-    if (bn == 256) return split_acc ? launch_tc_major<256, 2, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 2, 0>(g, ma, mb, a_3d, b_3d);
-    return split_acc ? launch_tc_major<128, 3, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 3, 0>(g, ma, mb, a_3d, b_3d);
+    const bool split_acc = (long)g_plan.kb_per_split * TC_BK > g_tc_split_k;
+    int rc;
+    if (bn == 256) rc = split_acc ? launch_tc_major<256, 2, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 2, 0>(g, ma, mb, a_3d, b_3d);
+    else rc = split_acc ? launch_tc_major<128, 3, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 3, 0>(g, ma, mb, a_3d, b_3d);
+    if (g_plan.partial) tt_dev_free(g_plan.partial);
+    g_plan.splits = 1; g_plan.partial = nullptr;
+    return rc;
 }

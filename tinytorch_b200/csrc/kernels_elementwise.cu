@@ -258,26 +258,62 @@ __device__ __forceinline__ float warp_sum(float v) {
  * is read once per pass from L1/L2-resident lines; a row whose maximum is
  * -Inf becomes uniform.  NaN never wins the max, as in the reference. */
 #define SM_WARPS 8
-__global__ void __launch_bounds__(SM_WARPS * 32) softmax_kernel(float *o, const float *__restrict__ x,
+#define SM_REG 32            /* values a lane keeps in registers: rows of up to 1024 are read from memory once */
+
+/* Row statistics shared by softmax and the fused loss: loads the row (into
+ * registers when it fits), returns max and the sum of exp(x - max), leaves the
+ * exponentials in v[].  NaN never wins the max, as in the reference. */
+__device__ __forceinline__ void softmax_row(const float *__restrict__ xr, int N, int lane, float (&v)[SM_REG],
+                                            bool in_regs, float &mx, float &sum) {
+    mx = -INFINITY;
+    if (in_regs) {
+        #pragma unroll
+        for (int i = 0; i < SM_REG; i++) {
+            int j = lane + 32 * i;
+            v[i] = j < N ? xr[j] : -INFINITY;
+            if (v[i] > mx) mx = v[i];
+        }
+    } else {
+        for (int j = lane; j < N; j += 32) { float t = xr[j]; if (t > mx) mx = t; }
+    }
+    mx = warp_max(mx);
+    sum = 0.0f;
+    if (mx == -INFINITY) return;
+    if (in_regs) {
+        #pragma unroll
+        for (int i = 0; i < SM_REG; i++) {
+            int j = lane + 32 * i;
+            v[i] = j < N ? expf(v[i] - mx) : 0.0f;
+            sum += v[i];
+        }
+    } else {
+        for (int j = lane; j < N; j += 32) sum += expf(xr[j] - mx);
+    }
+    sum = warp_sum(sum);
+}
+
+__global__ void __launch_bounds__(SM_WARPS * 32) softmax_kernel(float *__restrict__ o, const float *__restrict__ x,
                                                                   long rows, int N) {
     int lane = threadIdx.x & 31;
     long row = (long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
     long rstride = (long)gridDim.x * SM_WARPS;
+    const bool in_regs = N <= 32 * SM_REG;
     for (; row < rows; row += rstride) {
         const float *xr = x + row * N;
         float *orow = o + row * N;
-        float mx = -INFINITY;
-        for (int j = lane; j < N; j += 32) { float v = xr[j]; if (v > mx) mx = v; }
-        mx = warp_max(mx);
+        float v[SM_REG], mx, sum;
+        softmax_row(xr, N, lane, v, in_regs, mx, sum);
         if (mx == -INFINITY) {
             float u = 1.0f / (float)N;
             for (int j = lane; j < N; j += 32) orow[j] = u;
             continue;
         }
-        float sum = 0.0f;
-        for (int j = lane; j < N; j += 32) sum += expf(xr[j] - mx);
-        sum = warp_sum(sum);
-        for (int j = lane; j < N; j += 32) orow[j] = expf(xr[j] - mx) / sum;
+        if (in_regs) {
+            #pragma unroll
+            for (int i = 0; i < SM_REG; i++) { int j = lane + 32 * i; if (j < N) orow[j] = v[i] / sum; }
+        } else {
+            for (int j = lane; j < N; j += 32) orow[j] = expf(xr[j] - mx) / sum;
+        }
     }
 }
 void k_softmax(float *o, const float *x, long rows, int N) {
@@ -322,26 +358,36 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_xent_kernel(const float
     int lane = threadIdx.x & 31;
     long row = (long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
     long rstride = (long)gridDim.x * SM_WARPS;
+    const bool in_regs = N <= 32 * SM_REG;
     for (; row < rows; row += rstride) {
         const float *zr = z + row * N;
-        int y = (int)labels[row];
-        float mx = -INFINITY;
-        for (int j = lane; j < N; j += 32) { float v = zr[j]; if (v > mx) mx = v; }
-        mx = warp_max(mx);
+        float *drow = dz + row * N;
+        const int y = (int)labels[row];
+        float v[SM_REG], mx, sum;
+        softmax_row(zr, N, lane, v, in_regs, mx, sum);
         float py;
         if (mx == -INFINITY) {
             float u = 1.0f / (float)N;
-            for (int j = lane; j < N; j += 32) dz[row * N + j] = (u - (j == y ? 1.0f : 0.0f)) * scale;
+            for (int j = lane; j < N; j += 32) drow[j] = (u - (j == y ? 1.0f : 0.0f)) * scale;
             py = u;
         } else {
-            float sum = 0.0f;
-            for (int j = lane; j < N; j += 32) sum += expf(zr[j] - mx);
-            sum = warp_sum(sum);
             float mine = 0.0f;
-            for (int j = lane; j < N; j += 32) {
-                float p = expf(zr[j] - mx) / sum;
-                if (j == y) mine = p;
-                dz[row * N + j] = (p - (j == y ? 1.0f : 0.0f)) * scale;
+            if (in_regs) {
+                #pragma unroll
+                for (int i = 0; i < SM_REG; i++) {
+                    int j = lane + 32 * i;
+                    if (j < N) {
+                        float p = v[i] / sum;
+                        if (j == y) mine = p;
+                        drow[j] = (p - (j == y ? 1.0f : 0.0f)) * scale;
+                    }
+                }
+            } else {
+                for (int j = lane; j < N; j += 32) {
+                    float p = expf(zr[j] - mx) / sum;
+                    if (j == y) mine = p;
+                    drow[j] = (p - (j == y ? 1.0f : 0.0f)) * scale;
+                }
             }
             py = warp_sum(mine);
         }
@@ -395,7 +441,20 @@ __global__ void __launch_bounds__(CS_COLS * CS_ROWS / 4) colsum_partial_kernel(c
     int r1 = r0 + rows_per_slab < M ? r0 + rows_per_slab : M;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     bool vec = ((ldg & 3) == 0) && ((((uintptr_t)g) & 15u) == 0) && (col + 3 < N);
-    for (int r = r0 + ry; r < r1; r += CS_ROWS) {
+    int r = r0 + ry;
+    if (vec) {
+        /* four independent 128-bit loads in flight per thread */
+        for (; r + 3 * CS_ROWS < r1; r += 4 * CS_ROWS) {
+            const float *row = g + (long)r * ldg + col;
+            float4 a = *(const float4 *)row, b = *(const float4 *)(row + (long)CS_ROWS * ldg);
+            float4 c = *(const float4 *)(row + 2l * CS_ROWS * ldg), d = *(const float4 *)(row + 3l * CS_ROWS * ldg);
+            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+            acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+            acc.x += c.x; acc.y += c.y; acc.z += c.z; acc.w += c.w;
+            acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+        }
+    }
+    for (; r < r1; r += CS_ROWS) {
         const float *row = g + (long)r * ldg;
         if (vec) {
             float4 v = *(const float4 *)(row + col);

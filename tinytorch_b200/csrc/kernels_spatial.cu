@@ -30,32 +30,49 @@ static inline int grid_for(long items) {
 
 /* col[(c,kh,kw), (n,ho,wo)] = x[n, c, ho*sh-ph+kh, wo*sw-pw+kw] or 0
  * (src/ops_spatial.c:37-69; same map at src/autograd.c:371-404).
- * One thread per col element, wo fastest: reads and writes are both runs of
- * consecutive addresses for stride 1. */
+ * One block row per row of col, four consecutive columns per thread (one
+ * 128-bit store), wo fastest: reads and writes are both runs of consecutive
+ * addresses for stride 1, and the index decode is 32-bit. */
 __global__ void __launch_bounds__(TPB) im2col_kernel(const float *__restrict__ x, int N, int C, int H, int W,
                                                       int HH, int WW, int ph, int pw, int sh, int sw,
                                                       int Ho, int Wo, float *__restrict__ col) {
-    long sp = (long)Ho * Wo, ncol = (long)N * sp;
-    long total = (long)C * HH * WW * ncol;
-    long stride = (long)gridDim.x * blockDim.x;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        long c = i / ncol, r = i - c * ncol;
-        int n = (int)(r / sp);
-        int s = (int)(r - (long)n * sp);
-        int ho = s / Wo, wo = s - ho * Wo;
-        int kw = (int)(c % WW), kh = (int)((c / WW) % HH), ci = (int)(c / ((long)HH * WW));
-        int row = ho * sh - ph + kh, q = wo * sw - pw + kw;
-        float v = 0.0f;
-        if (row >= 0 && row < H && q >= 0 && q < W)
-            v = x[(((long)n * C + ci) * H + row) * W + q];
-        col[i] = v;
+    /* blockIdx.y = row of col (c_im, kh, kw); each thread produces four consecutive columns */
+    const int c = blockIdx.y;
+    const int kw = c % WW, kh = (c / WW) % HH, ci = c / (HH * WW);
+    const int sp = Ho * Wo;
+    const long ncol = (long)N * sp;
+    const long r0 = ((long)blockIdx.x * TPB + threadIdx.x) * 4;
+    if (r0 >= ncol) return;
+    float *dst = col + (long)c * ncol + r0;
+    int n = (int)(r0 / sp);
+    int s = (int)(r0 - (long)n * sp);
+    int ho = s / Wo, wo = s - ho * Wo;
+    float v[4];
+    #pragma unroll
+    for (int j = 0; j < 4; j++) {
+        v[j] = 0.0f;
+        if (r0 + j < ncol) {
+            const int row = ho * sh - ph + kh, q = wo * sw - pw + kw;
+            if (row >= 0 && row < H && q >= 0 && q < W)
+                v[j] = x[(((long)n * C + ci) * H + row) * W + q];
+        }
+        if (++wo == Wo) { wo = 0; if (++ho == Ho) { ho = 0; n++; } }
+    }
+    if (r0 + 3 < ncol && ((ncol & 3) == 0) && ((((uintptr_t)col) & 15u) == 0)) {
+        *(float4 *)dst = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        #pragma unroll
+        for (int j = 0; j < 4; j++) if (r0 + j < ncol) dst[j] = v[j];
     }
 }
 void k_im2col(const float *x, int N, int C, int H, int W, int HH, int WW,
               int ph, int pw, int sh, int sw, int Ho, int Wo, float *col) {
-    long total = (long)C * HH * WW * N * Ho * Wo;
+    const long ncol = (long)N * Ho * Wo;
+    const int kc = C * HH * WW;
+    const long total = ncol * kc;
+    dim3 grid((unsigned)((ncol + 4 * TPB - 1) / (4 * TPB)), (unsigned)kc);
     tt_trace_begin(TTB_K_SPATIAL);
-    LAUNCH(im2col_kernel, grid_for(total), TPB, 0, x, N, C, H, W, HH, WW, ph, pw, sh, sw, Ho, Wo, col);
+    LAUNCH(im2col_kernel, grid, TPB, 0, x, N, C, H, W, HH, WW, ph, pw, sh, sw, Ho, Wo, col);
     tt_trace_end(TTB_K_SPATIAL, 4.0 * ((double)total + (double)N * C * H * W));
 }
 
@@ -63,31 +80,30 @@ void k_im2col(const float *x, int N, int C, int H, int W, int HH, int WW,
  * x[n,ci,h,w] receives col[(ci,kh,kw),(n,ho,wo)] for every (kh,kw) with
  * ho*sh-ph+kh == h and wo*sw-pw+kw == w.  The reference adds them with
  * (kh,kw) ascending (its outer loop is c = (ci,kh,kw)); so does this. */
+template <bool UNIT_STRIDE>
 __global__ void __launch_bounds__(TPB) col2im_kernel(const float *__restrict__ col, int N, int C, int H, int W,
                                                       int HH, int WW, int ph, int pw, int sh, int sw,
                                                       int Ho, int Wo, float *__restrict__ x) {
-    long sp = (long)Ho * Wo, ncol = (long)N * sp;
-    long total = (long)N * C * H * W;
-    long stride = (long)gridDim.x * blockDim.x;
+    const long sp = (long)Ho * Wo, ncol = (long)N * sp;
+    const long total = (long)N * C * H * W;
+    const long stride = (long)gridDim.x * blockDim.x;
+    const int HW = H * W;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        int w = (int)(i % W);
-        long t = i / W;
-        int h = (int)(t % H); t /= H;
-        int ci = (int)(t % C);
-        int n = (int)(t / C);
+        const long plane = i / HW;                      /* n*C + ci */
+        const int pix = (int)(i - plane * HW);
+        const int h = pix / W, w = pix - h * W;
+        const int n = (int)(plane / C), ci = (int)(plane - (long)n * C);
+        const float *src = col + ((long)ci * HH * WW) * ncol + (long)n * sp;
         float acc = 0.0f;
         for (int kh = 0; kh < HH; kh++) {
-            int hn = h + ph - kh;
-            if (hn < 0 || hn % sh) continue;
-            int ho = hn / sh;
-            if (ho >= Ho) continue;
+            int ho = h + ph - kh;
+            if (!UNIT_STRIDE) { if (ho < 0 || ho % sh) continue; ho /= sh; }
+            if (ho < 0 || ho >= Ho) continue;
             for (int kw = 0; kw < WW; kw++) {
-                int wn = w + pw - kw;
-                if (wn < 0 || wn % sw) continue;
-                int wo = wn / sw;
-                if (wo >= Wo) continue;
-                long c = ((long)ci * HH + kh) * WW + kw;
-                acc = acc + col[c * ncol + (long)n * sp + (long)ho * Wo + wo];
+                int wo = w + pw - kw;
+                if (!UNIT_STRIDE) { if (wo < 0 || wo % sw) continue; wo /= sw; }
+                if (wo < 0 || wo >= Wo) continue;
+                acc = acc + src[(long)(kh * WW + kw) * ncol + (long)ho * Wo + wo];
             }
         }
         x[i] = acc;
@@ -97,49 +113,52 @@ void k_col2im(const float *col, int N, int C, int H, int W, int HH, int WW,
               int ph, int pw, int sh, int sw, int Ho, int Wo, float *x) {
     long total = (long)N * C * H * W;
     tt_trace_begin(TTB_K_SPATIAL);
-    LAUNCH(col2im_kernel, grid_for(total), TPB, 0, col, N, C, H, W, HH, WW, ph, pw, sh, sw, Ho, Wo, x);
+    if (sh == 1 && sw == 1)
+        LAUNCH(col2im_kernel<true>, grid_for(total), TPB, 0, col, N, C, H, W, HH, WW, ph, pw, sh, sw, Ho, Wo, x);
+    else
+        LAUNCH(col2im_kernel<false>, grid_for(total), TPB, 0, col, N, C, H, W, HH, WW, ph, pw, sh, sw, Ho, Wo, x);
     tt_trace_end(TTB_K_SPATIAL, 4.0 * ((double)total + (double)C * HH * WW * N * Ho * Wo));
 }
 
-/* out[n,f,i] = om[f, n*sp+i] + bias[f]   (src/ops_spatial.c:105-119) */
-__global__ void __launch_bounds__(TPB) conv_unpermute_bias_kernel(const float *__restrict__ om, const float *__restrict__ bias,
-                                                                   int N, int F, long sp, float *__restrict__ out) {
-    long total = (long)N * F * sp;
-    long stride = (long)gridDim.x * blockDim.x;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        long s = i % sp;
-        long t = i / sp;
-        int f = (int)(t % F);
-        long n = t / F;
-        float b = bias ? bias[f] : 0.0f;
-        out[i] = om[(long)f * N * sp + n * sp + s] + b;
+/* The two permutes around the convolution GEMMs move whole planes of sp floats:
+ *   unpermute: out[n,f,:] = om[f, n*sp : (n+1)*sp] + bias[f]   (src/ops_spatial.c:105-119)
+ *   permute:   gp[f, n*sp : (n+1)*sp] = g[n,f,:]               (src/autograd.c:494-501)
+ * blockIdx.y is the plane (n*F + f); threads run along the plane, 128 bits at a time. */
+template <bool TO_NCHW>
+__global__ void __launch_bounds__(TPB) conv_plane_kernel(const float *__restrict__ src, const float *__restrict__ bias,
+                                                          int N, int F, int sp, float *__restrict__ dst) {
+    const int plane = blockIdx.y;
+    const int n = plane / F, f = plane - n * F;
+    const long nchw = (long)plane * sp, fnhw = ((long)f * N + n) * sp;
+    const float *in = src + (TO_NCHW ? fnhw : nchw);
+    float *out = dst + (TO_NCHW ? nchw : fnhw);
+    const float b = (TO_NCHW && bias) ? bias[f] : 0.0f;
+    const bool vec = ((sp & 3) == 0) && ((((uintptr_t)src) & 15u) == 0) && ((((uintptr_t)dst) & 15u) == 0);
+    if (vec) {
+        for (int i = (blockIdx.x * TPB + threadIdx.x) * 4; i < sp; i += gridDim.x * TPB * 4) {
+            float4 v = *(const float4 *)(in + i);
+            if (TO_NCHW) { v.x = v.x + b; v.y = v.y + b; v.z = v.z + b; v.w = v.w + b; }
+            *(float4 *)(out + i) = v;
+        }
+    } else {
+        for (int i = blockIdx.x * TPB + threadIdx.x; i < sp; i += gridDim.x * TPB)
+            out[i] = TO_NCHW ? in[i] + b : in[i];
     }
+}
+static dim3 plane_grid(int N, int F, long sp) {
+    long bx = (sp + 4 * TPB - 1) / (4 * TPB);
+    if (bx > 64) bx = 64;
+    return dim3((unsigned)bx, (unsigned)(N * F));
 }
 void k_conv_unpermute_bias(const float *om, const float *bias, int N, int F, long sp, float *out) {
-    long total = (long)N * F * sp;
     tt_trace_begin(TTB_K_SPATIAL);
-    LAUNCH(conv_unpermute_bias_kernel, grid_for(total), TPB, 0, om, bias, N, F, sp, out);
-    tt_trace_end(TTB_K_SPATIAL, 8.0 * (double)total);
-}
-
-/* gp[f, n*sp+i] = g[n,f,i]   (src/autograd.c:494-501) */
-__global__ void __launch_bounds__(TPB) conv_permute_kernel(const float *__restrict__ g, int N, int F, long sp,
-                                                            float *__restrict__ gp) {
-    long total = (long)N * F * sp;
-    long stride = (long)gridDim.x * blockDim.x;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        long s = i % sp;
-        long t = i / sp;
-        long n = t % N;
-        long f = t / N;
-        gp[i] = g[(n * F + f) * sp + s];
-    }
+    LAUNCH(conv_plane_kernel<true>, plane_grid(N, F, sp), TPB, 0, om, bias, N, F, (int)sp, out);
+    tt_trace_end(TTB_K_SPATIAL, 8.0 * (double)N * F * sp);
 }
 void k_conv_permute(const float *g, int N, int F, long sp, float *gp) {
-    long total = (long)N * F * sp;
     tt_trace_begin(TTB_K_SPATIAL);
-    LAUNCH(conv_permute_kernel, grid_for(total), TPB, 0, g, N, F, sp, gp);
-    tt_trace_end(TTB_K_SPATIAL, 8.0 * (double)total);
+    LAUNCH(conv_plane_kernel<false>, plane_grid(N, F, sp), TPB, 0, g, nullptr, N, F, (int)sp, gp);
+    tt_trace_end(TTB_K_SPATIAL, 8.0 * (double)N * F * sp);
 }
 
 /* db[f] = sum over n, ho, wo of g[n,f,ho,wo]   (src/autograd.c:467-482).
@@ -276,11 +295,40 @@ __global__ void __launch_bounds__(TPB) maxpool_bwd_kernel(const float *__restric
         dx[i] = acc;
     }
 }
+/* Windows that tile the plane exactly (stride == pool, no leftover rows or columns):
+ * one thread owns one window, finds its arg-max and writes the whole window -- the
+ * gradient at the winner, zero elsewhere.  Same values as the gather above (each
+ * element belongs to exactly one window), a quarter of the index arithmetic. */
+__global__ void __launch_bounds__(TPB) maxpool_bwd_tiled_kernel(const float *__restrict__ x, const float *__restrict__ g, long NC,
+                                                                 int H, int W, int ph, int pw, int Ho, int Wo,
+                                                                 float *__restrict__ dx) {
+    const long total = NC * Ho * Wo;
+    const long stride = (long)gridDim.x * blockDim.x;
+    const int sp = Ho * Wo;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long nc = i / sp;
+        const int s = (int)(i - nc * sp);
+        const int ho = s / Wo, wo = s - ho * Wo;
+        const float *plane = x + nc * H * W;
+        float best; int bh, bw;
+        window_argmax(plane, W, ho * ph, wo * pw, ph, pw, best, bh, bw);
+        const float gv = g[i];
+        float *out = dx + nc * H * W;
+        for (int kh = 0; kh < ph; kh++)
+            for (int kw = 0; kw < pw; kw++) {
+                const int hh = ho * ph + kh, ww = wo * pw + kw;
+                out[(long)hh * W + ww] = (hh == bh && ww == bw) ? 0.0f + gv : 0.0f;
+            }
+    }
+}
 void k_maxpool_bwd(const float *x, const float *g, long NC, int H, int W, int ph, int pw,
                    int sh, int sw, int Ho, int Wo, float *dx) {
     long total = NC * H * W;
     tt_trace_begin(TTB_K_SPATIAL);
-    LAUNCH(maxpool_bwd_kernel, grid_for(total), TPB, 0, x, g, NC, H, W, ph, pw, sh, sw, Ho, Wo, dx);
+    if (sh == ph && sw == pw && Ho * ph == H && Wo * pw == W)
+        LAUNCH(maxpool_bwd_tiled_kernel, grid_for(NC * Ho * Wo), TPB, 0, x, g, NC, H, W, ph, pw, Ho, Wo, dx);
+    else
+        LAUNCH(maxpool_bwd_kernel, grid_for(total), TPB, 0, x, g, NC, H, W, ph, pw, sh, sw, Ho, Wo, dx);
     tt_trace_end(TTB_K_SPATIAL, 4.0 * (2.0 * (double)total + (double)NC * Ho * Wo));
 }
 

@@ -24,7 +24,27 @@ static int same_shape(const Tensor *a, const Tensor *b) {
 static int tc_wanted(const GemmArgs *g) {
     if (g_tt.gemm_path == 2) return 0;
     if (g_tt.gemm_path == 1) return 1;
-    return g->M >= 96 && g->N >= 32 && g->K >= 32 && (long)g->M * g->N * g->K >= (1l << 21);
+    return g->M >= 16 && g->N >= 8 && g->K >= 8 && (long)g->M * g->N * g->K >= (1l << 21);
+}
+
+/* TMA needs 16-byte aligned rows.  A small operand whose pitch is not a multiple of four
+ * floats (a [32,27] convolution filter bank, a [K,10] classifier weight) is copied into
+ * pool scratch with a padded pitch; large ones are left to the exact kernel. */
+static const float *repitched(const float *src, long rows, long cols, long *pitch, float **scratch) {
+    *scratch = nullptr;
+    if ((*pitch & 3) == 0 && ((((uintptr_t)src) & 15u) == 0)) return src;
+    if (rows * cols > (4l << 20)) return nullptr;
+    long np = (cols + 3) & ~3l;
+    float *buf = (float *)tt_dev_alloc(sizeof(float) * (size_t)rows * np);
+    if (!buf) return nullptr;
+    if (cudaMemcpy2DAsync(buf, np * sizeof(float), src, *pitch * sizeof(float), cols * sizeof(float), rows,
+                          cudaMemcpyDeviceToDevice, g_tt.stream) != cudaSuccess) {
+        cudaGetLastError();
+        tt_dev_free(buf);
+        return nullptr;
+    }
+    *scratch = buf; *pitch = np;
+    return buf;
 }
 
 int tt_gemm(const GemmArgs *g) {
@@ -34,7 +54,15 @@ int tt_gemm(const GemmArgs *g) {
         if (!g->ta) core.K = g->K - 1; else core.M = g->M - 1;
         core.a_pad_ones = 0;
     }
-    int use_tc = core.M > 0 && core.K > 0 && tc_wanted(&core) && gemm_tc_usable(&core);
+    float *sa = nullptr, *sb = nullptr;
+    int use_tc = core.M > 0 && core.K > 0 && tc_wanted(&core);
+    if (use_tc && !gemm_tc_usable(&core) && g_tt.gemm_path != 1) {
+        const float *a = repitched(core.A, core.ta ? core.K : core.M, core.ta ? core.M : core.K, &core.lda, &sa);
+        const float *b = a ? repitched(core.B, core.tb ? core.N : core.K, core.tb ? core.K : core.N, &core.ldb, &sb) : nullptr;
+        if (a && b) { core.A = a; core.B = b; }
+    }
+    use_tc = use_tc && gemm_tc_usable(&core);
+    struct Cleanup { float *a, *b; ~Cleanup() { if (a) tt_dev_free(a); if (b) tt_dev_free(b); } } cleanup = {sa, sb};
     if (g_tt.gemm_path == 1 && !use_tc) {
         tt_set_error("gemm: tensor-core path forced but the shape cannot be fed by TMA");
         return -1;
@@ -42,7 +70,7 @@ int tt_gemm(const GemmArgs *g) {
     if (!use_tc) return gemm_simt(g);
     if (g->a_pad_ones && !g->ta) {
         if (g->tb) return gemm_simt(g);                 /* bias row must be a row of B */
-        core.bias = g->B + (long)core.K * g->ldb;        /* the ones column times the last row of B */
+        core.bias = g->B + (long)core.K * g->ldb;        /* the ones column times the last row of B (always the caller's B) */
         return gemm_tc(&core);
     }
     if (g->a_pad_ones && g->ta) {

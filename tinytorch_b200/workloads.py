@@ -143,19 +143,23 @@ def mlp_step_reference_style(ns, x, y, ws, lr=0.1, global_batch=None, return_pre
     return {"loss": loss, "logits": logits_v, "probs": p, "grads": grads, "weights": new_ws, "pre": pre}
 
 
-def cnn_forward(ns, keep, xn, pn):
+def cnn_forward(ns, keep, xn, pn, pre=None):
     h = keep(xn.conv2d(pn["w1"], pn["b1"], stride=1, pad=1))
+    if pre is not None:
+        pre["z1"] = h
     h = keep(h.relu())
     h = keep(h.maxpool2d(2, 2))
     h = keep(h.conv2d(pn["w2"], pn["b2"], stride=1, pad=1))
+    if pre is not None:
+        pre["z2"] = h
     h = keep(h.relu())
     return keep(h.maxpool2d(2, 2))
 
 
-def cnn_step_reference_style(ns, x, y, params, global_batch=None):
+def cnn_step_reference_style(ns, x, y, params, global_batch=None, return_pre=False):
     """One forward + backward of the benchmark CNN in the style of
     tests/gate_cifar_cnn.py:101-111,160-185.  Returns loss, logits and the
-    gradient of every parameter."""
+    gradient of every parameter; with return_pre also the three pre-activations."""
     Node = ns.Node
     batch = x.shape[0]
     gb = global_batch or batch
@@ -167,9 +171,13 @@ def cnn_step_reference_style(ns, x, y, params, global_batch=None):
 
     pn = {k: keep(Node.leaf(v, True)) for k, v in params.items()}
     xn = keep(Node.leaf(x, False))
-    h = cnn_forward(ns, keep, xn, pn)
+    pre_nodes = {} if return_pre else None
+    h = cnn_forward(ns, keep, xn, pn, pre_nodes)
     h = keep(h.reshape((batch, int(np.prod(h.value_tensor().shape[1:])))))
-    h = keep(keep(keep(h.padones()).matmul(pn["fc1"])).relu())
+    h = keep(keep(h.padones()).matmul(pn["fc1"]))
+    if return_pre:
+        pre_nodes["z3"] = h
+    h = keep(h.relu())
     logits = keep(keep(h.padones()).matmul(pn["fc2"]))
     probs = keep(logits.softmax())
     p = probs.value()
@@ -177,9 +185,10 @@ def cnn_step_reference_style(ns, x, y, params, global_batch=None):
     logits.backward((p - onehot(y, p.shape[1])) / gb)
     grads = {k: n.grad() for k, n in pn.items()}
     logits_v = logits.value()
+    pre = {k: n.value() for k, n in pre_nodes.items()} if return_pre else None
     for n in nodes:
         n.release()
-    return {"loss": loss, "logits": logits_v, "grads": grads}
+    return {"loss": loss, "logits": logits_v, "grads": grads, "pre": pre}
 
 
 def gemm_fwd_bwd(ns, a, b, dc):
