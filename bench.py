@@ -180,38 +180,38 @@ def workload_config(n_gpus):
 
 
 # ------------------------------------------------------------------ our arm
-def gemm_block(ns, peaks, cases=((1024, 20), (4096, 5))):
-    """Forward + backward GEMM throughput (C = A*B, dA = dC*B^T, dB = A^T*dC) on
-    square problems, L2 flushed between repetitions."""
+def gemm_block(ns, peaks, cases=((1024, 5), (4096, 5))):
+    """Forward + backward GEMM throughput (C = A*B, dA = dC*B^T, dB = A^T*dC) on square
+    problems.  Each timed pass runs over enough independent operand sets that the pass as a
+    whole touches more than L2 holds (300 MB), back to back, so that small problems are
+    timed on the GPU and not on the host's launch path."""
     out = []
     tf32_peak = peaks["bf16_tflops"] / 2.0
-    flush = ns.Tensor.zeros((64 * 1024 * 1024,))          # 256 MB > 126 MB of L2
     for n, reps in cases:
-        a, b, dc = W.config_gemm(n, 1 if n == 1024 else 4)
-        an, bn = ns.Node.leaf(a, True), ns.Node.leaf(b, True)
-        dct = ns.Tensor.from_np(dc)
+        sets = max(1, -(-300 * 1024 * 1024 // (3 * n * n * 4)))
+        ops = []
+        for i in range(sets):
+            a, b, dc = W.config_gemm(n, 1000 + i) if i else W.config_gemm(n, 1 if n == 1024 else 4)
+            ops.append((ns.Node.leaf(a, True), ns.Node.leaf(b, True), ns.Tensor.from_np(dc)))
         times = []
         for r in range(reps + 3):
-            one = ns.Tensor(ns.checked(ns.LIB.tt_addscalar(flush.ptr, 1.0), "flush"))
-            one.release()
             e0, e1 = ns.LIB.ttb_event_create(), ns.LIB.ttb_event_create()
             ns.LIB.ttb_event_record(e0)
-            c = an.matmul(bn)
-            c.backward(dct)
+            for an, bn, dct in ops:
+                c = an.matmul(bn)
+                c.backward(dct)
+                c.release(); an.zero_grad(); bn.zero_grad()
             ns.LIB.ttb_event_record(e1)
-            ms = ns.LIB.ttb_event_elapsed_ms(e0, e1)
+            ms = ns.LIB.ttb_event_elapsed_ms(e0, e1) / sets
             ns.LIB.ttb_event_destroy(e0); ns.LIB.ttb_event_destroy(e1)
-            c.release(); an.zero_grad(); bn.zero_grad()
             if r >= 3:
                 times.append(ms)
         med = statistics.median(times)
         tflops = 6.0 * n ** 3 / (med * 1e-3) / 1e12
-        out.append({"shape": [n, n, n], "ms": med, "tflops": tflops, "frac_of_tf32_peak": tflops / tf32_peak,
-                    "tensor_pipe_frac_estimate": 3 * tflops / tf32_peak})
-        for t in (an, bn):
-            t.release()
-        dct.release()
-    flush.release()
+        out.append({"shape": [n, n, n], "ms": med, "operand_sets_per_pass": sets, "tflops": tflops,
+                    "frac_of_tf32_peak": tflops / tf32_peak, "tensor_pipe_frac_estimate": 3 * tflops / tf32_peak})
+        for an, bn, dct in ops:
+            an.release(); bn.release(); dct.release()
     return out
 
 
@@ -273,25 +273,30 @@ def run_ours(args):
         if n:
             classes[name] = {"ms_per_step": ms / args.steps, "launches_per_step": n / args.steps}
 
-    # -------- end to end: pinned host inputs in, loss out, every step
+    # -------- end to end: pinned host inputs in, loss out, every step.  Two device buffers used in
+    # turn: the copy of step i+1's shard runs on the copy stream under step i's kernels (the input
+    # pipeline a training loop would run); every step's inputs still cross PCIe inside the timed region.
     x_pin, y_pin = ns.pinned_array(xs.shape), ns.pinned_array(ys.shape)
     x_pin[...] = xs; y_pin[...] = ys
+    xbuf = [ns.Tensor.zeros(xs.shape), ns.Tensor.zeros(xs.shape)]
+    ybuf = [ns.Tensor.zeros(ys.shape), ns.Tensor.zeros(ys.shape)]
 
-    def e2e_step():
-        xt, yt = ns.Tensor.from_np(x_pin), ns.Tensor.from_np(y_pin)
-        loss = trainer.step(xt, yt)
-        v = float(loss.to_np()[0])              # device -> host read of the step's result
-        for t in (xt, yt, loss):
-            t.release()
+    def e2e_run(n):
+        ns.upload_async(xbuf[0], x_pin); ns.upload_async(ybuf[0], y_pin)
+        v = None
+        for i in range(n):
+            if i + 1 < n:
+                ns.upload_async(xbuf[(i + 1) % 2], x_pin); ns.upload_async(ybuf[(i + 1) % 2], y_pin)
+            loss = trainer.step(xbuf[i % 2], ybuf[i % 2])
+            v = float(loss.to_np()[0])          # device -> host read of the step's result
+            loss.release()
         return v
 
-    for _ in range(min(args.warmup, 3)):
-        e2e_step()
+    e2e_run(min(args.warmup, 3))
     ns.sync(); D.barrier()
     t0 = time.perf_counter()
     ns.LIB.ttb_event_record(e0)
-    for _ in range(args.steps):
-        e2e_step()
+    e2e_run(args.steps)
     ns.LIB.ttb_event_record(e1)
     e2e_ms = ns.LIB.ttb_event_elapsed_ms(e0, e1)
     ns.sync(); D.barrier()
@@ -362,7 +367,8 @@ def run_gemm(args):
     line = {"metric": "gemm_fwd_bwd_tflops", "value": res["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
             "steps": args.steps, "warmup": 3, "ms_per_step": res["ms"], "higher_is_better": True,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"isolated GEMM forward + backward, square {args.gemm_n}", "l2": "flushed between repetitions"},
+            "config": {"workload": f"isolated GEMM forward + backward, square {args.gemm_n}",
+                       "l2": f"{res['operand_sets_per_pass']} independent operand sets per timed pass, more than L2 holds"},
             "roofline": {"bound": "tensor", "achieved": res["tflops"], "peak": peaks["bf16_tflops"] / 2.0, "unit": "TFLOP/s",
                          "frac": res["frac_of_tf32_peak"], "traffic": None,
                          "peak_source": f"{peak_kind} bf16_tflops / 2 (burst: kernel timed alone)"},

@@ -41,6 +41,15 @@ float      *ttb_device_ptr(Tensor *t);
 void       *ttb_pinned_alloc(size_t bytes);
 void        ttb_pinned_free(void *p);
 
+/* Input pipeline.  Overwrite an existing tensor with `src` (numel floats, best from
+ * ttb_pinned_alloc) on a separate copy stream: the transfer runs under whatever
+ * kernels are executing, is ordered after all work enqueued before the call, and
+ * the tensor's next use waits for it.  With two tensors used in turn, the upload
+ * of batch i+1 hides behind the step on batch i.  Stands in for the per-step
+ * normalise/gather/upload of the gate scripts (tests/gate_mnist_mlp.py:107-111).
+ * `src` must stay untouched until the tensor has been used.  Returns 0 or -1. */
+int         ttb_upload_async(Tensor *dst, const float *src);
+
 /* CUDA-event timing on the library's own stream. */
 void       *ttb_event_create(void);
 void        ttb_event_record(void *ev);

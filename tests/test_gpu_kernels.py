@@ -115,6 +115,27 @@ def test_host_writes_through_tt_data_are_seen(tt):
     t.release(); o.release()
 
 
+def test_async_upload_is_ordered_with_compute(tt):
+    """ttb_upload_async overwrites a tensor on the copy stream: work enqueued before the call
+    still sees the old contents, work enqueued after sees the new ones."""
+    n = 1 << 22
+    a = np.full(n, 1.0, np.float32)
+    pin = tt.pinned_array((n,))
+    t = tt.Tensor.from_np(a)
+    outs = []
+    for k in range(4):
+        before = tt.Tensor(tt.checked(tt.LIB.tt_mulscalar(t.ptr, 2.0), "tt_mulscalar"))   # reads the old payload
+        pin[...] = float(k + 10)
+        tt.upload_async(t, pin)
+        after = tt.Tensor(tt.checked(tt.LIB.tt_mulscalar(t.ptr, 2.0), "tt_mulscalar"))    # must wait for the copy
+        want_before = 2.0 if k == 0 else 2.0 * (k + 9)
+        assert np.all(before.to_np() == want_before), k
+        assert np.all(after.to_np() == 2.0 * (k + 10)), k
+        assert np.all(t.to_np() == float(k + 10))
+        before.release(); after.release()
+    t.release()
+
+
 @pytest.mark.parametrize("shape", [(5,), (3, 6), (2, 3, 4), (128, 10), (64, 1000), (7, 1031), (4, 5000)])
 def test_softmax_forward_backward(tt, orc, shape):
     rng = np.random.default_rng(3)

@@ -80,6 +80,7 @@ EXT_ABI = {
     "ttb_device_ptr": (VP, [VP]),
     "ttb_pinned_alloc": (VP, [ctypes.c_size_t]),
     "ttb_pinned_free": (None, [VP]),
+    "ttb_upload_async": (CI, [VP, F32P]),
     "ttb_event_create": (VP, []),
     "ttb_event_record": (None, [VP]),
     "ttb_event_elapsed_ms": (ctypes.c_float, [VP, VP]),
@@ -343,6 +344,14 @@ def bind(path=None):
             ns._pinned.append(ptr)
             return arr
 
+        def upload_async(tensor, arr):
+            """Queue a host -> device copy of `arr` (same element count) into `tensor`."""
+            arr = np.ascontiguousarray(arr, dtype=np.float32)
+            if arr.size != tensor.numel():
+                raise ValueError("tinytorch: ttb_upload_async size mismatch")
+            status(lib.ttb_upload_async(tensor.ptr, arr.ctypes.data_as(F32P)), "ttb_upload_async")
+
+        ns.upload_async = upload_async
         ns._pinned = []
         ns.pinned_array = pinned_array
         ns.matmul_nt = lambda x, y: op("ttb_matmul_nt", x.ptr, y.ptr)

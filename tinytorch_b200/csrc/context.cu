@@ -9,7 +9,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-TTContext g_tt = {0, 0, 0, nullptr, nullptr, -1, -1, 0, 0};    /* -1: take the setting from the environment */
+TTContext g_tt = {0, 0, 0, nullptr, nullptr, nullptr, -1, -1, 0, 0};    /* -1: take the setting from the environment */
 
 static char g_err[512] = "";
 
@@ -59,7 +59,8 @@ static int ctx_open(int device) {
     g_tt.device = device;
     g_tt.sm_count = prop.multiProcessorCount;
     if (!tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.stream, cudaStreamNonBlocking), "cudaStreamCreate") ||
-        !tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.comm_stream, cudaStreamNonBlocking), "cudaStreamCreate")) {
+        !tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.comm_stream, cudaStreamNonBlocking), "cudaStreamCreate") ||
+        !tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.copy_stream, cudaStreamNonBlocking), "cudaStreamCreate")) {
         g_tt.ready = -1;
         return -1;
     }
@@ -105,6 +106,7 @@ extern "C" int ttb_sync(void) {
     if (tt_ctx_init() != 0) return -1;
     if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.stream), "cudaStreamSynchronize")) return -1;
     if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.comm_stream), "cudaStreamSynchronize(comm)")) return -1;
+    if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.copy_stream), "cudaStreamSynchronize(copy)")) return -1;
     if (gemm_tc_poll_status()) return -1;
     return 0;
 }

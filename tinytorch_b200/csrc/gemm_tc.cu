@@ -640,18 +640,38 @@ int gemm_tc(const GemmArgs *g) {
     const int num_kb = (g->K + TC_BK - 1) / TC_BK;
     const long tiles = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + bn - 1) / bn);
     g_plan.splits = 1; g_plan.kb_per_split = num_kb; g_plan.partial = nullptr;
+    long want = 1;
     if (g_tc_splitk && tiles * 2 <= g_tt.sm_count && num_kb >= 8) {
-        long want = g_tt.sm_count / tiles;
+        /* few tiles: as many slices as fill the machine */
+        want = g_tt.sm_count / tiles;
         if (want > num_kb / 4) want = num_kb / 4;
-        const long max_by_mem = (256l << 20) / ((long)g->M * g->N * 4 + 1);
-        if (want > max_by_mem) want = max_by_mem;
-        if (want >= 2) {
-            const int per = (int)((num_kb + want - 1) / want);
-            const int splits = (num_kb + per - 1) / per;
-            float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * g->M * g->N);
-            if (!scratch) return -1;
-            g_plan.splits = splits; g_plan.kb_per_split = per; g_plan.partial = scratch;
+    } else if (g_tc_splitk && num_kb >= 32) {
+        /* many tiles: the last wave may be mostly empty (512 tiles on 148 SMs run as 4 waves of
+         * work worth 3.46).  Two to four slices change the wave count; take the cut whose gain
+         * in occupancy outweighs writing and re-reading the partial products. */
+        const double sms = (double)g_tt.sm_count;
+        const double mma_us = 6.0 * g->M * (double)g->N * g->K / (sms * 4096.0 * 1.8e3 * 0.75);   /* microseconds at 75 % of the pipe */
+        double best = 1e30;
+        for (long sp = 1; sp <= 4; sp++) {
+            if (num_kb / sp < 16) break;
+            const double items = (double)tiles * sp;
+            const double waves = (double)((long)((items + sms - 1) / sms));
+            const double eff = items / (waves * sms);
+            const double extra_us = sp > 1 ? (2.0 * sp + 1.0) * g->M * (double)g->N * 4.0 / 5.0e6 + 6.0 : 0.0;
+            const double t = mma_us / eff + extra_us;
+            if (t < best * 0.98) { best = t; want = sp; }
         }
+    }
+    if (want >= 2) {
+        const long max_by_mem = (512l << 20) / ((long)g->M * g->N * 4 + 1);
+        if (want > max_by_mem) want = max_by_mem;
+    }
+    if (want >= 2) {
+        const int per = (int)((num_kb + want - 1) / want);
+        const int splits = (num_kb + per - 1) / per;
+        float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * g->M * g->N);
+        if (!scratch) return -1;
+        g_plan.splits = splits; g_plan.kb_per_split = per; g_plan.partial = scratch;
     }
     /* long reductions keep the cross terms in their own accumulator (see the kernel) */
     const bool split_acc = (long)g_plan.kb_per_split * TC_BK > g_tc_split_k;

@@ -260,19 +260,34 @@ __device__ __forceinline__ float warp_sum(float v) {
 #define SM_WARPS 8
 #define SM_REG 32            /* values a lane keeps in registers: rows of up to 1024 are read from memory once */
 
-/* Row statistics shared by softmax and the fused loss: loads the row (into
- * registers when it fits), returns max and the sum of exp(x - max), leaves the
- * exponentials in v[].  NaN never wins the max, as in the reference. */
+/* Element index of register slot i for this lane.  Vector form: the lane owns four
+ * consecutive values per 128-bit access (slots 4q..4q+3 hold elements 4*(lane+32q)..);
+ * scalar form: slot i holds element lane + 32*i. */
+__device__ __forceinline__ int sm_index(int i, int lane, bool vec) {
+    return vec ? 4 * (lane + 32 * (i >> 2)) + (i & 3) : lane + 32 * i;
+}
+
+/* Row statistics shared by softmax and the fused loss: loads the row (into registers
+ * when it fits), returns max and the sum of exp(x - max), leaves the exponentials in
+ * v[].  NaN never wins the max, as in the reference (src/ops.c:120-124). */
 __device__ __forceinline__ void softmax_row(const float *__restrict__ xr, int N, int lane, float (&v)[SM_REG],
-                                            bool in_regs, float &mx, float &sum) {
+                                            bool in_regs, bool vec, float &mx, float &sum) {
     mx = -INFINITY;
+    if (in_regs && vec) {
+        #pragma unroll
+        for (int q = 0; q < SM_REG / 4; q++) {
+            const int j = 4 * (lane + 32 * q);
+            float4 t = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            if (j < N) t = *(const float4 *)(xr + j);
+            v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+        }
+    } else if (in_regs) {
+        #pragma unroll
+        for (int i = 0; i < SM_REG; i++) { const int j = lane + 32 * i; v[i] = j < N ? xr[j] : -INFINITY; }
+    }
     if (in_regs) {
         #pragma unroll
-        for (int i = 0; i < SM_REG; i++) {
-            int j = lane + 32 * i;
-            v[i] = j < N ? xr[j] : -INFINITY;
-            if (v[i] > mx) mx = v[i];
-        }
+        for (int i = 0; i < SM_REG; i++) if (v[i] > mx) mx = v[i];
     } else {
         for (int j = lane; j < N; j += 32) { float t = xr[j]; if (t > mx) mx = t; }
     }
@@ -282,8 +297,7 @@ __device__ __forceinline__ void softmax_row(const float *__restrict__ xr, int N,
     if (in_regs) {
         #pragma unroll
         for (int i = 0; i < SM_REG; i++) {
-            int j = lane + 32 * i;
-            v[i] = j < N ? expf(v[i] - mx) : 0.0f;
+            v[i] = sm_index(i, lane, vec) < N ? expf(v[i] - mx) : 0.0f;
             sum += v[i];
         }
     } else {
@@ -292,25 +306,41 @@ __device__ __forceinline__ void softmax_row(const float *__restrict__ xr, int N,
     sum = warp_sum(sum);
 }
 
+/* Store the register-resident row: o[j] = f(v, j). */
+template <class F>
+__device__ __forceinline__ void sm_store(float *__restrict__ orow, int N, int lane, const float (&v)[SM_REG], bool vec, F f) {
+    if (vec) {
+        #pragma unroll
+        for (int q = 0; q < SM_REG / 4; q++) {
+            const int j = 4 * (lane + 32 * q);
+            if (j < N)
+                *(float4 *)(orow + j) = make_float4(f(v[4 * q], j), f(v[4 * q + 1], j + 1), f(v[4 * q + 2], j + 2), f(v[4 * q + 3], j + 3));
+        }
+    } else {
+        #pragma unroll
+        for (int i = 0; i < SM_REG; i++) { const int j = lane + 32 * i; if (j < N) orow[j] = f(v[i], j); }
+    }
+}
+
 __global__ void __launch_bounds__(SM_WARPS * 32) softmax_kernel(float *__restrict__ o, const float *__restrict__ x,
                                                                   long rows, int N) {
     int lane = threadIdx.x & 31;
     long row = (long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
     long rstride = (long)gridDim.x * SM_WARPS;
     const bool in_regs = N <= 32 * SM_REG;
+    const bool vec = in_regs && ((N & 3) == 0) && (((((uintptr_t)x) | ((uintptr_t)o)) & 15u) == 0);
     for (; row < rows; row += rstride) {
         const float *xr = x + row * N;
         float *orow = o + row * N;
         float v[SM_REG], mx, sum;
-        softmax_row(xr, N, lane, v, in_regs, mx, sum);
+        softmax_row(xr, N, lane, v, in_regs, vec, mx, sum);
         if (mx == -INFINITY) {
             float u = 1.0f / (float)N;
             for (int j = lane; j < N; j += 32) orow[j] = u;
             continue;
         }
         if (in_regs) {
-            #pragma unroll
-            for (int i = 0; i < SM_REG; i++) { int j = lane + 32 * i; if (j < N) orow[j] = v[i] / sum; }
+            sm_store(orow, N, lane, v, vec, [sum](float e, int) { return e / sum; });
         } else {
             for (int j = lane; j < N; j += 32) orow[j] = expf(xr[j] - mx) / sum;
         }
@@ -359,12 +389,13 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_xent_kernel(const float
     long row = (long)blockIdx.x * SM_WARPS + (threadIdx.x >> 5);
     long rstride = (long)gridDim.x * SM_WARPS;
     const bool in_regs = N <= 32 * SM_REG;
+    const bool vec = in_regs && ((N & 3) == 0) && (((((uintptr_t)z) | ((uintptr_t)dz)) & 15u) == 0);
     for (; row < rows; row += rstride) {
         const float *zr = z + row * N;
         float *drow = dz + row * N;
         const int y = (int)labels[row];
         float v[SM_REG], mx, sum;
-        softmax_row(zr, N, lane, v, in_regs, mx, sum);
+        softmax_row(zr, N, lane, v, in_regs, vec, mx, sum);
         float py;
         if (mx == -INFINITY) {
             float u = 1.0f / (float)N;
@@ -374,14 +405,8 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_xent_kernel(const float
             float mine = 0.0f;
             if (in_regs) {
                 #pragma unroll
-                for (int i = 0; i < SM_REG; i++) {
-                    int j = lane + 32 * i;
-                    if (j < N) {
-                        float p = v[i] / sum;
-                        if (j == y) mine = p;
-                        drow[j] = (p - (j == y ? 1.0f : 0.0f)) * scale;
-                    }
-                }
+                for (int i = 0; i < SM_REG; i++) if (sm_index(i, lane, vec) == y) mine = v[i] / sum;
+                sm_store(drow, N, lane, v, vec, [sum, scale, y](float e, int j) { return (e / sum - (j == y ? 1.0f : 0.0f)) * scale; });
             } else {
                 for (int j = lane; j < N; j += 32) {
                     float p = expf(zr[j] - mx) / sum;

@@ -118,6 +118,10 @@ extern "C" void tt_release(Tensor *t) {
     if (!t) return;
     if (--t->refcount > 0) return;
     TTensor *x = TT(t);
+    if (x->ready) {
+        if (x->ready_pending && g_tt.ready == 1) cudaStreamWaitEvent(g_tt.stream, x->ready, 0);   /* the free is stream-ordered */
+        cudaEventDestroy(x->ready);
+    }
     if (x->dev) tt_dev_free(x->dev);
     if (x->lazy_src) tt_release(&x->lazy_src->pub);
     record_free(x);
@@ -140,10 +144,19 @@ static int materialise(TTensor *t) {
     return 1;
 }
 
+/* An upload queued by ttb_upload_async must land before anything else touches the payload. */
+static int await_upload(TTensor *t) {
+    if (!t->ready_pending) return 1;
+    if (!tt_cuda_ok(cudaStreamWaitEvent(g_tt.stream, t->ready, 0), "cudaStreamWaitEvent(upload)")) return 0;
+    t->ready_pending = 0;
+    return 1;
+}
+
 float *tt_dev_ro(const Tensor *ct) {
     TTensor *t = TT(ct);
     if (!t) return nullptr;
     if (!materialise(t)) return nullptr;
+    if (!await_upload(t)) return nullptr;
     if (t->host_exposed) {
         /* The caller holds the mirror and may have written to it. */
         if (!tt_cuda_ok(cudaMemcpyAsync(t->dev, t->pub.data, sizeof(float) * (size_t)t->pub.numel,
@@ -163,10 +176,33 @@ float *tt_dev_rw(Tensor *ct) {
 
 extern "C" float *ttb_device_ptr(Tensor *t) { return t ? tt_dev_ro(t) : nullptr; }
 
+/* Input pipeline: copy host data into an EXISTING tensor on the copy stream, so that the
+ * transfer of the next batch runs under the kernels of the current one.  The copy is ordered
+ * after all compute work enqueued so far (which may still read the old contents); the
+ * tensor's next use on the compute stream waits for it. */
+extern "C" int ttb_upload_async(Tensor *dst, const float *src) {
+    TTensor *t = TT(dst);
+    if (!t || !src) { tt_set_error("ttb_upload_async: NULL argument"); return -1; }
+    if (!materialise(t) || !await_upload(t)) return -1;
+    static cudaEvent_t fence = nullptr;
+    if (!fence && !tt_cuda_ok(cudaEventCreateWithFlags(&fence, cudaEventDisableTiming), "cudaEventCreate")) return -1;
+    if (!t->ready && !tt_cuda_ok(cudaEventCreateWithFlags(&t->ready, cudaEventDisableTiming), "cudaEventCreate")) return -1;
+    if (!tt_cuda_ok(cudaEventRecord(fence, g_tt.stream), "cudaEventRecord") ||
+        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.copy_stream, fence, 0), "cudaStreamWaitEvent") ||
+        !tt_cuda_ok(cudaMemcpyAsync(t->dev, src, sizeof(float) * (size_t)t->pub.numel, cudaMemcpyHostToDevice,
+                                    g_tt.copy_stream), "cudaMemcpyAsync(H2D)") ||
+        !tt_cuda_ok(cudaEventRecord(t->ready, g_tt.copy_stream), "cudaEventRecord"))
+        return -1;
+    t->ready_pending = 1;
+    t->dev_valid = 1; t->host_valid = 0; t->host_exposed = 0;
+    return 0;
+}
+
 extern "C" float *tt_data(const Tensor *ct) {
     TTensor *t = TT(ct);
     if (!t) return nullptr;
     if (!materialise(t)) return nullptr;
+    if (!await_upload(t)) return nullptr;
     size_t bytes = sizeof(float) * (size_t)t->pub.numel;
     if (!t->pub.data) {
         t->pub.data = (float *)malloc(bytes);

@@ -22,6 +22,8 @@ typedef struct TTensor {
     uint8_t host_exposed;  /* tt_data() handed the mirror out since the last upload */
     uint8_t lazy_kind;     /* payload not produced yet: TT_LAZY_* */
     struct TTensor *lazy_src;   /* retained source of a deferred payload */
+    cudaEvent_t ready;     /* upload on the copy stream that the next device use must wait for */
+    uint8_t ready_pending;
 } TTensor;
 
 static inline TTensor *TT(const Tensor *t) { return (TTensor *)t; }
@@ -33,6 +35,7 @@ typedef struct TTContext {
     int          sm_count;
     cudaStream_t stream;       /* all compute */
     cudaStream_t comm_stream;  /* NCCL all-reduce */
+    cudaStream_t copy_stream;  /* asynchronous input uploads */
     int          gemm_path;    /* 0 auto, 1 tensor core, 2 exact fp32 */
     int          fuse_padones; /* fold padones into the adjoining GEMM */
     int          trace;
