@@ -235,7 +235,7 @@ def run_ours(args):
     b = hi - lo
     xs, ys = np.ascontiguousarray(x[lo:hi]), y[lo:hi].astype(np.float32)
     del x
-    trainer = W.MLPTrainer(ns, ws, lr=LR, global_batch=GLOBAL_BATCH)
+    trainer = W.MLPTrainer(ns, ws, lr=LR, global_batch=GLOBAL_BATCH, fused_sgd=os.environ.get("TT_FUSED_SGD", "1") != "0")
     x_dev, y_dev = ns.Tensor.from_np(xs), ns.Tensor.from_np(ys)
 
     def resident_step():
@@ -252,10 +252,12 @@ def run_ours(args):
     e0, e1 = ns.LIB.ttb_event_create(), ns.LIB.ttb_event_create()
     ns.LIB.ttb_event_record(e0)
     last = None
+    host_t0 = time.perf_counter()
     for _ in range(args.steps):
         if last is not None:
             last.release()
         last = resident_step()
+    host_enqueue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps   # the host only enqueues; it runs ahead of the GPU
     ns.LIB.ttb_event_record(e1)
     ms_total = ns.LIB.ttb_event_elapsed_ms(e0, e1)
     ns.sync(); D.barrier()
@@ -320,7 +322,7 @@ def run_ours(args):
         "config": workload_config(world),
         "fwd_bwd_tflops": flops_step / (ms_step * 1e-3) / 1e12,
         "fwd_bwd_tflops_frac_of_tf32_peak": flops_step / (ms_step * 1e-3) / 1e12 / (tf32_peak * world),
-        "final_loss": final_loss,
+        "final_loss": final_loss, "host_enqueue_ms_per_step": host_enqueue_ms,
         "roofline": {
             "kernel": "gemm_tc_kernel (tcgen05.mma kind::tf32, 3xTF32 split, TMA-staged)",
             "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
@@ -507,6 +509,7 @@ def run_cnn(args):
 
 
 def main():
+    global GLOBAL_BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -514,11 +517,14 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--ref-batch", type=int, default=256,
                     help="samples per CPU step of the reference arm / CPU baseline (a slice of the global batch)")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                    help="tuning aid: a smaller global batch reproduces the per-GPU shapes of a larger job on fewer GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--workload", choices=["mlp", "gemm", "kernels", "cnn"], default="mlp")
     ap.add_argument("--gemm-n", type=int, default=4096)
     args = ap.parse_args()
+    GLOBAL_BATCH = args.global_batch
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":

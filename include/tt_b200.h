@@ -159,6 +159,12 @@ int     ttb_dist_unique_id(char id_out[128]);
 int     ttb_dist_init(int rank, int world, const char id[128]);
 int     ttb_dist_world(void);                        /* 1 when not initialised */
 void    ag_mark_param(AGNode *leaf, int on);
+/* Fuse plain SGD into the backward pass: as soon as the gradient of `leaf` is final (and,
+ * for a marked parameter, summed over the ranks) the library applies value -= lr * grad,
+ * on the communication stream when there is one, so the update of layer L runs under the
+ * backward kernels of the layers below it.  lr <= 0 switches it off.  Same arithmetic as
+ * ttb_sgd_step; call ttb_dist_join before the next forward pass. */
+void    ag_param_sgd(AGNode *leaf, float lr);
 int     ttb_dist_allreduce(Tensor *t);               /* sum over ranks, in place, async */
 int     ttb_dist_join(void);
 void    ttb_dist_finalize(void);

@@ -176,15 +176,17 @@ def test_device_resident_trainer_equals_gate_script_style(tt):
         r = W.mlp_step_reference_style(tt, x, y, ref_ws, lr=0.1)
         ref_ws = r["weights"]
         losses.append(r["loss"])
-    tr = W.MLPTrainer(tt, ws, lr=0.1)
     xt, yt = tt.Tensor.from_np(x), tt.Tensor.from_np(y.astype(np.float32))
-    got_losses = []
-    for _ in range(3):
-        loss = tr.step(xt, yt)
-        got_losses.append(float(loss.to_np()[0]))
-        loss.release()
-    for a, b in zip(tr.weights(), ref_ws):
-        assert rel_err(a, b) <= 1e-5
-    assert np.allclose(got_losses, losses, rtol=1e-5)
+    for fused in (True, False):            # SGD fused into the backward pass, or as separate calls
+        tr = W.MLPTrainer(tt, ws, lr=0.1, fused_sgd=fused)
+        got_losses = []
+        for _ in range(3):
+            loss = tr.step(xt, yt)
+            got_losses.append(float(loss.to_np()[0]))
+            loss.release()
+        for a, b in zip(tr.weights(), ref_ws):
+            assert rel_err(a, b) <= 1e-5
+        assert np.allclose(got_losses, losses, rtol=1e-5)
+        tr.close()
     assert losses[-1] < losses[0]
-    tr.close(); xt.release(); yt.release()
+    xt.release(); yt.release()

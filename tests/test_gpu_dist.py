@@ -23,7 +23,7 @@ ns.status(ns.LIB.ttb_init(local), "ttb_init")
 D.connect(ns, rank, world)
 assert ns.LIB.ttb_dist_world() == world
 rng = np.random.default_rng(5)
-dims, B = (256, 384, 128, 40), 512
+dims, B = (2048, 384, 128, 40), 512      # first layer wide enough for the chunked dW + all-reduce path
 x = rng.standard_normal((B, dims[0])).astype(np.float32)
 y = rng.integers(0, dims[-1], size=B)
 ws = [W.dense_weight(rng, dims[i], dims[i + 1]) for i in range(3)]

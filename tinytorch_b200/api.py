@@ -112,6 +112,7 @@ EXT_ABI = {
     "ttb_dist_init": (CI, [CI, CI, ctypes.c_char_p]),
     "ttb_dist_world": (CI, []),
     "ag_mark_param": (None, [VP, CI]),
+    "ag_param_sgd": (None, [VP, ctypes.c_float]),
     "ttb_dist_allreduce": (CI, [VP]),
     "ttb_dist_join": (CI, []),
     "ttb_dist_finalize": (None, []),
@@ -292,6 +293,9 @@ def bind(path=None):
 
         def mark_param(self, on=True):
             lib.ag_mark_param(self.ptr, 1 if on else 0)
+
+        def param_sgd(self, lr):
+            lib.ag_param_sgd(self.ptr, float(lr))
 
         def release(self):
             if self.ptr:

@@ -40,6 +40,8 @@ struct AGNode {
     int     pending;       /* consumers not yet processed in the running pass */
     int     is_param;      /* gradient is all-reduced across ranks when final */
     int     fused_pad;     /* matmul that consumed its padones parent virtually */
+    float   sgd_lr;        /* > 0: value -= sgd_lr * grad as soon as the gradient is final */
+    int     reduced_in_rule;   /* the rule that produced the gradient already reduced/applied it in chunks */
 };
 
 /* ---- construction ----------------------------------------------------------*/
@@ -178,6 +180,7 @@ extern "C" Tensor *ag_value(const AGNode *n) { return n ? n->val : nullptr; }
 extern "C" Tensor *ag_grad(const AGNode *n) { return n ? n->grad : nullptr; }
 extern "C" int ag_requires_grad(const AGNode *n) { return n ? n->requires_grad : 0; }
 extern "C" void ag_mark_param(AGNode *leaf, int on) { if (leaf) leaf->is_param = on ? 1 : 0; }
+extern "C" void ag_param_sgd(AGNode *leaf, float lr) { if (leaf) leaf->sgd_lr = lr > 0.0f ? lr : 0.0f; }
 extern "C" void ag_zero_grad(AGNode *n) {
     if (!n || !n->grad) return;
     tt_release(n->grad);
@@ -222,6 +225,30 @@ static float *grad_target(AGNode *p, int *accumulate) {
     return TT(t)->dev;
 }
 
+/* Elements [off, off+count) of a parameter's gradient are final: sum them over the ranks
+ * (marked parameters, communicator present) and, for a parameter with a fused optimiser,
+ * apply w -= lr * g right behind the reduction on the same stream.  With a communicator
+ * both run on the communication stream, under the backward kernels still to come;
+ * ttb_dist_join orders the compute stream after them. */
+void tt_dist_note_comm_work(void);
+static void param_grad_ready(AGNode *p, long off, long count) {
+    if (!p->grad || count <= 0) return;
+    const int dist = tt_dist_active() && p->is_param;
+    if (!dist && p->sgd_lr <= 0.0f) return;
+    float *g = tt_dev_rw(p->grad);
+    if (!g) return;
+    if (dist) tt_dist_allreduce_range(g + off, (size_t)count);
+    if (p->sgd_lr > 0.0f) {
+        float *w = tt_dev_rw(p->val);
+        if (!w) return;
+        cudaStream_t keep = g_tt.stream;
+        if (dist) g_tt.stream = g_tt.comm_stream;
+        k_sgd(w + off, g + off, p->sgd_lr, count);
+        g_tt.stream = keep;
+        if (dist) tt_dist_note_comm_work();
+    }
+}
+
 /* ---- backward rules ----------------------------------------------------------*/
 static void bw_mul(AGNode *n) {              /* src/autograd.c:290-298 */
     take(n->parents[0], tt_mul(n->grad, n->parents[1]->val));
@@ -256,7 +283,29 @@ static void bw_matmul(AGNode *n) {
             const float *px = tt_dev_ro(x->val);
             int acc;
             float *dst = px ? grad_target(b, &acc) : nullptr;
-            if (dst) {
+            static int dp_chunks = -1;
+            if (dp_chunks < 0) { const char *e = getenv("TT_DP_CHUNKS"); dp_chunks = e && *e ? atoi(e) : 2; if (dp_chunks < 1) dp_chunks = 1; }
+            if (dst && dp_chunks > 1 && tt_dist_active() && b->is_param && b->pending == 1 && Kr >= 2048 &&
+                !x->requires_grad) {
+                /* Data parallel, first layer (its input needs no gradient, so this is the last GEMM
+                 * of the pass and nothing is left to hide its all-reduce behind): produce the
+                 * gradient in row blocks (TT_DP_CHUNKS, default two) and hand each to the all-reduce
+                 * as soon as it exists; only the last block's reduction is exposed.  Measured on the
+                 * per-GPU shapes of the 8-GPU job: 2.38 -> 2.26 ms per step with two blocks, slower
+                 * with four (more, smaller collectives). */
+                const int rows_per = ((Kr / dp_chunks + 127) / 128) * 128;
+                for (int r0 = 0; r0 < Kr; r0 += rows_per) {
+                    const int r1 = r0 + rows_per < Kr ? r0 + rows_per : Kr;
+                    const int last = (r1 == Kr);
+                    memset(&g, 0, sizeof g);
+                    g.ta = 1; g.a_pad_ones = last; g.M = r1 - r0 + last; g.N = N; g.K = M;
+                    g.A = px + r0; g.lda = Kr; g.B = pg; g.ldb = N; g.C = dst + (long)r0 * N; g.ldc = N;
+                    g.accumulate = acc; g.rule = 1;
+                    if (tt_gemm(&g) != 0) break;
+                    param_grad_ready(b, (long)r0 * N, (long)(r1 - r0 + last) * N);
+                }
+                b->reduced_in_rule = 1;
+            } else if (dst) {
                 memset(&g, 0, sizeof g);
                 g.ta = 1; g.a_pad_ones = 1; g.M = Kr + 1; g.N = N; g.K = M;
                 g.A = px; g.lda = Kr; g.B = pg; g.ldb = N; g.C = dst; g.ldc = N;
@@ -488,17 +537,16 @@ static void run_backward(AGNode *out, const float *seed_host, const Tensor *seed
             k_fill(pd, numel, 1.0f);
         }
         if (seeded) {
-            for (size_t i = 0; i < ord.n; i++) ord.v[i]->pending = 0;
+            for (size_t i = 0; i < ord.n; i++) { ord.v[i]->pending = 0; ord.v[i]->reduced_in_rule = 0; }
             for (size_t i = 0; i < ord.n; i++)
                 for (int k = 0; k < ord.v[i]->nparents; k++) ord.v[i]->parents[k]->pending++;
-            const int dist = tt_dist_active();
             for (size_t i = ord.n; i-- > 0;) {
                 AGNode *n = ord.v[i];
                 if (n->grad && n->nparents > 0) backward_rule(n);
                 for (int k = 0; k < n->nparents; k++) {
                     AGNode *p = n->parents[k];
-                    if (--p->pending == 0 && dist && p->is_param && p->grad)
-                        tt_dist_allreduce_async(p->grad);
+                    if (--p->pending == 0 && p->grad && !p->reduced_in_rule && (p->is_param || p->sgd_lr > 0.0f))
+                        param_grad_ready(p, 0, p->grad->numel);
                 }
             }
         }

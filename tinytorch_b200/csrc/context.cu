@@ -9,7 +9,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-TTContext g_tt = {0, 0, 0, nullptr, nullptr, nullptr, -1, -1, 0, 0};    /* -1: take the setting from the environment */
+TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, 0, 0};    /* -1: take the setting from the environment */
 
 static char g_err[512] = "";
 
@@ -58,6 +58,8 @@ static int ctx_open(int device) {
     }
     g_tt.device = device;
     g_tt.sm_count = prop.multiProcessorCount;
+    g_tt.gemm_sms = env_int("TT_GEMM_SMS", g_tt.sm_count);
+    if (g_tt.gemm_sms < 1 || g_tt.gemm_sms > g_tt.sm_count) g_tt.gemm_sms = g_tt.sm_count;
     if (!tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.stream, cudaStreamNonBlocking), "cudaStreamCreate") ||
         !tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.comm_stream, cudaStreamNonBlocking), "cudaStreamCreate") ||
         !tt_cuda_ok(cudaStreamCreateWithFlags(&g_tt.copy_stream, cudaStreamNonBlocking), "cudaStreamCreate")) {

@@ -594,7 +594,7 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     p.a_3d = a_3d; p.b_3d = b_3d;
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
     int tiles = ((g->M + TC_BM - 1) / TC_BM) * ((g->N + BN - 1) / BN) * p.splits;
-    int grid = tiles < g_tt.sm_count ? tiles : g_tt.sm_count;
+    int grid = tiles < g_tt.gemm_sms ? tiles : g_tt.gemm_sms;
     tt_trace_begin(TTB_K_GEMM_TC);
     kern<<<grid, TC_THREADS, smem, g_tt.stream>>>(ma, mb, p);
     g_tt.launches++;
@@ -623,7 +623,7 @@ int gemm_tc(const GemmArgs *g) {
     if (tc_setup() != 0) return -1;
     /* 128x256 tiles unless that leaves most SMs idle */
     const long tiles256 = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + 255) / 256);
-    int bn = (tiles256 * 10 < (long)g_tt.sm_count * 7 || g->N <= 128) ? 128 : 256;
+    int bn = (tiles256 * 10 < (long)g_tt.gemm_sms * 7 || g->N <= 128) ? 128 : 256;
     if (g_tc_force_bn == 128 || g_tc_force_bn == 256) bn = g_tc_force_bn;
     CUtensorMap ma, mb;
     int a_3d = 0, b_3d = 0;
@@ -641,15 +641,15 @@ int gemm_tc(const GemmArgs *g) {
     const long tiles = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + bn - 1) / bn);
     g_plan.splits = 1; g_plan.kb_per_split = num_kb; g_plan.partial = nullptr;
     long want = 1;
-    if (g_tc_splitk && tiles * 2 <= g_tt.sm_count && num_kb >= 8) {
+    if (g_tc_splitk && tiles * 2 <= g_tt.gemm_sms && num_kb >= 8) {
         /* few tiles: as many slices as fill the machine */
-        want = g_tt.sm_count / tiles;
+        want = g_tt.gemm_sms / tiles;
         if (want > num_kb / 4) want = num_kb / 4;
     } else if (g_tc_splitk && num_kb >= 32) {
         /* many tiles: the last wave may be mostly empty (512 tiles on 148 SMs run as 4 waves of
          * work worth 3.46).  Two to four slices change the wave count; take the cut whose gain
          * in occupancy outweighs writing and re-reading the partial products. */
-        const double sms = (double)g_tt.sm_count;
+        const double sms = (double)g_tt.gemm_sms;
         const double mma_us = 6.0 * g->M * (double)g->N * g->K / (sms * 4096.0 * 1.8e3 * 0.75);   /* microseconds at 75 % of the pipe */
         double best = 1e30;
         for (long sp = 1; sp <= 4; sp++) {

@@ -33,6 +33,7 @@ typedef struct TTContext {
     int          ready;        /* 1 after a successful init, -1 after a failed one */
     int          device;
     int          sm_count;
+    int          gemm_sms;     /* CTAs a persistent GEMM may occupy: all SMs, fewer while NCCL kernels share the GPU */
     cudaStream_t stream;       /* all compute */
     cudaStream_t comm_stream;  /* NCCL all-reduce */
     cudaStream_t copy_stream;  /* asynchronous input uploads */
@@ -137,5 +138,6 @@ int gemm_tc_poll_status(void);                  /* non-zero (reason stored) when
 /* dist.cu: called by the backward pass when a marked leaf's gradient is final. */
 int tt_dist_active(void);
 int tt_dist_allreduce_async(Tensor *t);
+int tt_dist_allreduce_range(float *p, size_t count);     /* same, for a contiguous part of a gradient */
 
 #endif

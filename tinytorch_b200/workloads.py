@@ -212,16 +212,19 @@ class MLPTrainer:
 
     Needs the additive entry points, i.e. this library, not the reference."""
 
-    def __init__(self, ns, ws, lr=0.1, global_batch=None):
+    def __init__(self, ns, ws, lr=0.1, global_batch=None, fused_sgd=True):
         if not ns.has_ext:
             raise RuntimeError("MLPTrainer needs the ttb_* entry points")
         self.ns = ns
         self.lr = float(lr)
         self.global_batch = global_batch
+        self.fused_sgd = fused_sgd
         self.params = []
         for w in ws:
             n = ns.Node.leaf(w, True)
             n.mark_param(True)
+            if fused_sgd:
+                n.param_sgd(lr)       # the update rides behind each gradient's all-reduce
             self.params.append(n)
         self.dims = tuple([ws[0].shape[0] - 1] + [w.shape[1] for w in ws])
 
@@ -243,7 +246,8 @@ class MLPTrainer:
         h.backward(dlogits)
         ns.status(ns.LIB.ttb_dist_join(), "ttb_dist_join")
         for w in self.params:
-            ns.sgd_step(w.value_tensor(), w.grad_tensor(), self.lr)
+            if not self.fused_sgd:
+                ns.sgd_step(w.value_tensor(), w.grad_tensor(), self.lr)
             w.zero_grad()
         dlogits.release()
         for n in nodes:
