@@ -28,7 +28,7 @@
  *               mbarriers; owns the tensor-memory allocation.
  *   warps 10-13 epilogue: tcgen05.ld the finished accumulator (one of two,
  *               so the next tile's MMAs overlap), add bias / old C, store.
- * Tile 128 x BN x 32 (BN = 256 or 128), 128-byte swizzled rows everywhere.
+ * Tiles 128x256 (two stages) or 128x128 (three stages), K blocks of 32.
  *
  * Every wait is bounded: a wait that exceeds its cycle budget records a code
  * in a host-visible status word, raises a CTA-wide abort flag that all other
@@ -40,10 +40,9 @@
 #include <string.h>
 
 #define TC_BM 128
-#define TC_BK 32                 /* 32 fp32 = one 128-byte swizzle span */
+/* K block of a stage: 32 fp32 (128-byte rows) or 16 (64-byte rows, twice the stages) -- template parameter BK */
 #define TC_THREADS 448
 #define TC_SPLIT_THREADS 256
-#define TC_PREFETCH 6            /* K blocks the producer asks L2 for ahead of its loads */
 #define TC_EPI_THREADS 128
 #define TC_WAIT_CYCLES (1ll << 30)
 
@@ -86,6 +85,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             return false;
         }
     }
+}
+/* The same for a whole warp: one lane spins (381 spinning threads would spend shared-memory
+ * bandwidth the tensor core needs), then every lane checks once so that each thread has
+ * observed the phase itself.  Returns the same value in all lanes. */
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                               uint32_t *status, uint32_t code) {
+    bool got = true;
+    if ((threadIdx.x & 31) == 0) got = mbar_wait(bar, parity, abort_flag, status, code);
+    got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+    if (got) got = mbar_try(bar, parity);
+    return __all_sync(0xffffffffu, got);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
     asm volatile(
@@ -143,11 +153,13 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
  *                   (mode 1; TMA mode SWIZZLE_128B_ATOM_32B): 4-row groups 512
  *                   bytes apart (stride offset), boxes 4096 bytes apart (leading
  *                   offset); a K step of 8 rows advances the start by 1024 bytes. */
-template <int MN_MAJOR>
+template <int MN_MAJOR, int BK>
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
-    constexpr uint32_t lbo_bytes = MN_MAJOR ? 4096 : 16;
-    constexpr uint32_t sbo_bytes = MN_MAJOR ? 512 : 1024;
-    constexpr uint64_t mode = MN_MAJOR ? 1 : 2;
+    /* K-major rows are BK*4 bytes: 128-byte rows swizzle over 8 rows of 128 (mode 2), 64-byte rows over
+     * 8 rows of 64 (mode 4, TMA SWIZZLE_64B).  MN-major boxes hold BK k-rows of 128 bytes. */
+    constexpr uint32_t lbo_bytes = MN_MAJOR ? BK * 128 : 16;
+    constexpr uint32_t sbo_bytes = MN_MAJOR ? 512 : 8 * BK * 4;
+    constexpr uint64_t mode = MN_MAJOR ? 1 : (BK == 32 ? 2 : 4);
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3ffffu) >> 4);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
@@ -180,11 +192,12 @@ struct TcParams {
     uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
 };
 
-template <int A_MN, int B_MN, int BN, int STAGES, int SPLIT_ACC>
+template <int A_MN, int B_MN, int BN, int BK, int STAGES, int SPLIT_ACC>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
-    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 4;          /* 16 KB */
-    constexpr uint32_t B_BYTES = BN * TC_BK * 4;
+    constexpr uint32_t A_BYTES = TC_BM * BK * 4;
+    constexpr uint32_t B_BYTES = BN * BK * 4;
+    constexpr uint32_t BOX = BK * 128;                        /* one MN-major box: BK k-rows of 128 bytes */
     constexpr uint32_t HI_BYTES = A_BYTES + B_BYTES;         /* raw tiles of one stage */
     constexpr uint32_t STAGE_BYTES = 2 * HI_BYTES;           /* raw + lo */
     constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)A_MN << 15) |
@@ -197,6 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
      * error that grows with the number of MMAs into a LARGE accumulator; keeping the
      * cross terms (2^-11 of the result) apart removes two thirds of those. */
     constexpr int NACC = SPLIT_ACC ? 1 : 2;
+    constexpr int TC_PREFETCH = STAGES + (BK == 16 ? 8 : 4);   /* K blocks the producer asks L2 for ahead of its loads */
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -215,7 +229,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM;
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
-    const int num_kb = (p.K + TC_BK - 1) / TC_BK;
+    const int num_kb = (p.K + BK - 1) / BK;
     const int num_items = num_tiles * p.splits;          /* work items: (K slice, tile) */
     /* item -> first row, first column, K-block range, slice */
     auto decode = [&](int it, int &m0, int &n0, int &kb0, int &kb1, int &split) {
@@ -255,7 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int s = 0; uint32_t ph = 0;
             bool ok = true;
             auto prefetch = [&](int m0, int n0, int kb) {
-                const int k0 = kb * TC_BK;
+                const int k0 = kb * BK;
                 if (A_MN && p.a_3d) {
                     tma_prefetch_3d(&map_a, 0, k0, m0 / 32);
                 } else if (A_MN) {
@@ -291,13 +305,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
                     const uint32_t st = smem_base + s * STAGE_BYTES;
                     const uint32_t full = bar_full + 8 * s;
-                    const int k0 = kb * TC_BK;
+                    const int k0 = kb * BK;
                     mbar_expect_tx(full, HI_BYTES);
                     if (A_MN && p.a_3d) {
                         tma_load_3d(st, &map_a, full, 0, k0, m0 / 32);
                     } else if (A_MN) {
                         #pragma unroll
-                        for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * 4096, &map_a, full, m0 + 32 * b, k0);
+                        for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * BOX, &map_a, full, m0 + 32 * b, k0);
                     } else {
                         tma_load_2d(st, &map_a, full, k0, m0);
                     }
@@ -305,7 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tma_load_3d(st + A_BYTES, &map_b, full, 0, k0, n0 / 32);
                     } else if (B_MN) {
                         #pragma unroll
-                        for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * 4096, &map_b, full, n0 + 32 * b, k0);
+                        for (int b = 0; b < BN / 32; b++) tma_load_2d(st + A_BYTES + b * BOX, &map_b, full, n0 + 32 * b, k0);
                     } else {
                         tma_load_2d(st + A_BYTES, &map_b, full, k0, n0);
                     }
@@ -340,15 +354,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t a_lo = a_hi + HI_BYTES;
                     const uint32_t b_lo = b_hi + HI_BYTES;
                     #pragma unroll
-                    for (int ks = 0; ks < TC_BK / 8; ks++) {
+                    for (int ks = 0; ks < BK / 8; ks++) {
                         const uint32_t a_off = A_MN ? ks * 1024 : ks * 32;
                         const uint32_t b_off = B_MN ? ks * 1024 : ks * 32;
-                        const uint64_t da_hi = make_desc<A_MN>(a_hi + a_off);
-                        const uint64_t db_hi = make_desc<B_MN>(b_hi + b_off);
+                        const uint64_t da_hi = make_desc<A_MN, BK>(a_hi + a_off);
+                        const uint64_t db_hi = make_desc<B_MN, BK>(b_hi + b_off);
                         const uint32_t first = (kb > kb0 || ks > 0) ? 1u : 0u;
                         if (p.passes == 3) {
-                            const uint64_t da_lo = make_desc<A_MN>(a_lo + a_off);
-                            const uint64_t db_lo = make_desc<B_MN>(b_lo + b_off);
+                            const uint64_t da_lo = make_desc<A_MN, BK>(a_lo + a_off);
+                            const uint64_t db_lo = make_desc<B_MN, BK>(b_lo + b_off);
                             tc_mma_tf32(d_corr, da_lo, db_hi, IDESC, first);
                             tc_mma_tf32(d_corr, da_hi, db_lo, IDESC, 1u);
                             tc_mma_tf32(d_main, da_hi, db_hi, IDESC, SPLIT_ACC ? first : 1u);
@@ -373,8 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int m0, n0, kb0, kb1, split;
             decode(it, m0, n0, kb0, kb1, split);
             for (int kb = kb0; kb < kb1; kb++) {
-                const bool got = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 1);
-                if (!__all_sync(0xffffffffu, got)) { ok = false; break; }     /* keep the warp together */
+                if (!mbar_wait_warp(bar_full + 8 * s, ph, abort_flag, p.status, 1)) { ok = false; break; }
                 if (p.passes == 3) {
                     const uint8_t *hi = smem_gen + s * STAGE_BYTES;
                     #pragma unroll 4
@@ -404,8 +417,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             decode(it, m0, n0, kb0, kb1, split);
             float *cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
             const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0);
-            const bool got = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5);
-            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }         /* tcgen05.ld needs the whole warp */
+            if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5)) { ok = false; break; }   /* tcgen05.ld needs the whole warp */
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             float *crow = cbase + (long)row * ldc;
@@ -492,6 +504,7 @@ static EncodeTiledFn g_encode = nullptr;
 static uint32_t *g_status_host = nullptr;     /* mapped pinned word the kernel reports into */
 static uint32_t *g_status_dev = nullptr;
 static int g_tc_passes = 3;
+static int g_tc_force_bk = 0;        /* TT_TC_BK: tuning aid, 0 = by tile shape */
 static int g_tc_force_bn = 0;        /* TT_TC_BN: tuning aid, 0 = choose by tile count */
 static int g_tc_splitk = 1;          /* TT_TC_SPLITK=0: tuning aid, never cut the reduction across CTAs */
 static int g_tc_mn3d = 1;            /* TT_TC_MN3D=0: tuning aid, one TMA per 32 columns for MN-major tiles */
@@ -517,6 +530,8 @@ static int tc_setup(void) {
     if (e && *e) g_tc_splitk = atoi(e);
     e = getenv("TT_TC_MN3D");
     if (e && *e) g_tc_mn3d = atoi(e);
+    e = getenv("TT_TC_BK");
+    if (e && *e) g_tc_force_bk = atoi(e);
     e = getenv("TT_TC_BN");
     if (e && *e) g_tc_force_bn = atoi(e);
     e = getenv("TT_TC_SPLIT_K");
@@ -539,13 +554,15 @@ int gemm_tc_poll_status(void) {
 /* inner = contiguous extent, outer = number of rows, pitch in floats */
 static int encode_map(CUtensorMap *map, const float *base, long inner, long outer, long pitch, int box_inner, int box_outer,
                       int mn_major) {
+    /* K-major boxes are box_inner*4 bytes wide: 128 -> SWIZZLE_128B, 64 -> SWIZZLE_64B */
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
     cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                   : (box_inner == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { tt_set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return -1; }
     return 0;
@@ -555,10 +572,10 @@ static int encode_map(CUtensorMap *map, const float *base, long inner, long oute
  * {32 values, K rows, MN/32 column groups} with strides {4, pitch*4, 128} bytes.  A box
  * {32, 32, groups} then lands in shared memory group after group, 32 k-rows of 128 bytes
  * each -- the layout the kernel's MN-major descriptors expect -- with ONE copy per tile. */
-static int encode_map_mn3d(CUtensorMap *map, const float *base, long mn, long k, long pitch, int groups) {
+static int encode_map_mn3d(CUtensorMap *map, const float *base, long mn, long k, long pitch, int groups, int bk) {
     cuuint64_t dims[3] = {32, (cuuint64_t)k, (cuuint64_t)(mn / 32)};
     cuuint64_t strides[2] = {(cuuint64_t)pitch * sizeof(float), 128};
-    cuuint32_t box[3] = {32, 32, (cuuint32_t)groups};
+    cuuint32_t box[3] = {32, (cuuint32_t)bk, (cuuint32_t)groups};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
@@ -578,11 +595,11 @@ int gemm_tc_usable(const GemmArgs *g) {
 /* Split-K plan of the launch being prepared (host side, single caller thread). */
 static struct { int splits, kb_per_split; float *partial; } g_plan = {1, 0, nullptr};
 
-template <int A_MN, int B_MN, int BN, int STAGES, int SPLIT_ACC>
+template <int A_MN, int B_MN, int BN, int BK, int STAGES, int SPLIT_ACC>
 static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
-    constexpr size_t smem = (size_t)STAGES * 2 * (TC_BM * TC_BK * 4 + BN * TC_BK * 4) + 1024 + 8 * (3 * STAGES + 4) + 16;
+    constexpr size_t smem = (size_t)STAGES * 2 * (TC_BM * BK * 4 + BN * BK * 4) + 1024 + 8 * (3 * STAGES + 4) + 16;
     static bool configured = false;
-    auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES, SPLIT_ACC>;
+    auto kern = gemm_tc_kernel<A_MN, B_MN, BN, BK, STAGES, SPLIT_ACC>;
     if (!configured) {
         if (!tt_cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                         "cudaFuncSetAttribute(smem)")) return -1;
@@ -609,13 +626,13 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     return tt_cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch") ? 0 : -1;
 }
 
-template <int BN, int STAGES, int SPLIT_ACC>
+template <int BN, int BK, int STAGES, int SPLIT_ACC>
 static int launch_tc_major(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
     const int a_mn = g->ta ? 1 : 0, b_mn = g->tb ? 0 : 1;
-    if (!a_mn && !b_mn) return launch_tc<0, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
-    if (!a_mn && b_mn)  return launch_tc<0, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
-    if (a_mn && !b_mn)  return launch_tc<1, 0, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
-    return launch_tc<1, 1, BN, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
+    if (!a_mn && !b_mn) return launch_tc<0, 0, BN, BK, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
+    if (!a_mn && b_mn)  return launch_tc<0, 1, BN, BK, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
+    if (a_mn && !b_mn)  return launch_tc<1, 0, BN, BK, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
+    return launch_tc<1, 1, BN, BK, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
 }
 
 int gemm_tc(const GemmArgs *g) {
@@ -626,26 +643,31 @@ int gemm_tc(const GemmArgs *g) {
     int bn = (tiles256 * 10 < (long)g_tt.gemm_sms * 7 || g->N <= 128) ? 128 : 256;
     if (g_tc_force_bn == 128 || g_tc_force_bn == 256) bn = g_tc_force_bn;
     CUtensorMap ma, mb;
+    /* K blocks of 32 (two stages for 128x256 tiles, three for 128x128).  TT_TC_BK=16 selects 64-byte
+     * rows with twice the stages; measured equal (the kernel is bound by shared-memory bandwidth,
+     * not by pipeline depth), so it stays a tuning aid. */
+    int bk = 32;
+    if (g_tc_force_bk == 16 || g_tc_force_bk == 32) bk = g_tc_force_bk;
     int a_3d = 0, b_3d = 0;
     if (g->ta) {
-        if (g_tc_mn3d && g->M % 32 == 0 && encode_map_mn3d(&ma, g->A, g->M, g->K, g->lda, TC_BM / 32) == 0) a_3d = 1;
-        else if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, 32, 1)) return -1;
-    } else if (encode_map(&ma, g->A, g->K, g->M, g->lda, TC_BK, TC_BM, 0)) return -1;
+        if (g_tc_mn3d && g->M % 32 == 0 && encode_map_mn3d(&ma, g->A, g->M, g->K, g->lda, TC_BM / 32, bk) == 0) a_3d = 1;
+        else if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, bk, 1)) return -1;
+    } else if (encode_map(&ma, g->A, g->K, g->M, g->lda, bk, TC_BM, 0)) return -1;
     if (g->tb) {
-        if (encode_map(&mb, g->B, g->K, g->N, g->ldb, TC_BK, bn, 0)) return -1;
-    } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, bn / 32) == 0) b_3d = 1;
-    else if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, 32, 1)) return -1;
+        if (encode_map(&mb, g->B, g->K, g->N, g->ldb, bk, bn, 0)) return -1;
+    } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, bn / 32, bk) == 0) b_3d = 1;
+    else if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, bk, 1)) return -1;
     /* Split-K when the tiles alone leave most SMs idle and the reduction is long enough to cut:
      * slices of at least four K blocks, as many as fill the machine, partials in pool scratch. */
-    const int num_kb = (g->K + TC_BK - 1) / TC_BK;
+    const int num_kb = (g->K + bk - 1) / bk;
     const long tiles = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + bn - 1) / bn);
     g_plan.splits = 1; g_plan.kb_per_split = num_kb; g_plan.partial = nullptr;
     long want = 1;
-    if (g_tc_splitk && tiles * 2 <= g_tt.gemm_sms && num_kb >= 8) {
+    if (g_tc_splitk && tiles * 2 <= g_tt.gemm_sms && num_kb >= 2 * (128 / bk)) {
         /* few tiles: as many slices as fill the machine */
         want = g_tt.gemm_sms / tiles;
-        if (want > num_kb / 4) want = num_kb / 4;
-    } else if (g_tc_splitk && num_kb >= 32) {
+        if (want > num_kb / (128 / bk)) want = num_kb / (128 / bk);      /* slices of at least 128 along K */
+    } else if (g_tc_splitk && (long)num_kb * bk >= 1024) {
         /* many tiles: the last wave may be mostly empty (512 tiles on 148 SMs run as 4 waves of
          * work worth 3.46).  Two to four slices change the wave count; take the cut whose gain
          * in occupancy outweighs writing and re-reading the partial products. */
@@ -653,7 +675,7 @@ int gemm_tc(const GemmArgs *g) {
         const double mma_us = 6.0 * g->M * (double)g->N * g->K / (sms * 4096.0 * 1.8e3 * 0.75);   /* microseconds at 75 % of the pipe */
         double best = 1e30;
         for (long sp = 1; sp <= 4; sp++) {
-            if (num_kb / sp < 16) break;
+            if ((long)(num_kb / sp) * bk < 512) break;
             const double items = (double)tiles * sp;
             const double waves = (double)((long)((items + sms - 1) / sms));
             const double eff = items / (waves * sms);
@@ -674,10 +696,12 @@ int gemm_tc(const GemmArgs *g) {
         g_plan.splits = splits; g_plan.kb_per_split = per; g_plan.partial = scratch;
     }
     /* long reductions keep the cross terms in their own accumulator (see the kernel) */
-    const bool split_acc = (long)g_plan.kb_per_split * TC_BK > g_tc_split_k;
+    const bool split_acc = (long)g_plan.kb_per_split * bk > g_tc_split_k;
     int rc;
-    if (bn == 256) rc = split_acc ? launch_tc_major<256, 2, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 2, 0>(g, ma, mb, a_3d, b_3d);
-    else rc = split_acc ? launch_tc_major<128, 3, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 3, 0>(g, ma, mb, a_3d, b_3d);
+    if (bn == 256 && bk == 16) rc = split_acc ? launch_tc_major<256, 16, 4, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 16, 4, 0>(g, ma, mb, a_3d, b_3d);
+    else if (bn == 256)        rc = split_acc ? launch_tc_major<256, 32, 2, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 32, 2, 0>(g, ma, mb, a_3d, b_3d);
+    else if (bk == 16)         rc = split_acc ? launch_tc_major<128, 16, 6, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 16, 6, 0>(g, ma, mb, a_3d, b_3d);
+    else                       rc = split_acc ? launch_tc_major<128, 32, 3, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 32, 3, 0>(g, ma, mb, a_3d, b_3d);
     if (g_plan.partial) tt_dev_free(g_plan.partial);
     g_plan.splits = 1; g_plan.partial = nullptr;
     return rc;
