@@ -94,7 +94,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     bool got = true;
     if ((threadIdx.x & 31) == 0) got = mbar_wait(bar, parity, abort_flag, status, code);
     got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
-    if (got) got = mbar_try(bar, parity);
+    if (got) got = mbar_wait(bar, parity, abort_flag, status, code);     /* immediate: the phase is complete */
     return __all_sync(0xffffffffu, got);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
@@ -183,6 +183,7 @@ struct TcParams {
     const float *bias;
     int accumulate;
     int passes;              /* 3 = full split, 1 = hi*hi only (bring-up aid) */
+    int nosplit;             /* tuning aid: issue the three MMAs but skip producing the lo tiles (wrong numbers) */
     int a_3d, b_3d;          /* MN-major operand described by a rank-3 map: one TMA per tile instead of one per 32 columns */
     /* Split-K: the reduction is cut into `splits` slices of kb_per_split K blocks; slice s of a tile
      * writes its partial product to partial + s*M*N (row pitch N) and a second kernel adds the slices
@@ -388,7 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             decode(it, m0, n0, kb0, kb1, split);
             for (int kb = kb0; kb < kb1; kb++) {
                 if (!mbar_wait_warp(bar_full + 8 * s, ph, abort_flag, p.status, 1)) { ok = false; break; }
-                if (p.passes == 3) {
+                if (p.passes == 3 && !p.nosplit) {
                     const uint8_t *hi = smem_gen + s * STAGE_BYTES;
                     #pragma unroll 4
                     for (uint32_t c = st_tid; c < HI_BYTES / 16; c += TC_SPLIT_THREADS) {
@@ -480,6 +481,340 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+/* ======================================================================================
+ * CTA-pair variant: tcgen05.mma.cta_group::2, tile 256x256 over two SMs.
+ *
+ * The one-CTA kernel is bound by shared-memory bandwidth: per K block of 32 the tensor core
+ * reads 144 KB of operands (three MMAs per K step, A and B each time), the split pass moves
+ * 96 KB and TMA writes 48 KB -- more than one SM's shared memory delivers in the 1536 cycles
+ * the MMAs take.  In a pair each CTA stages its own 128 rows of A and HALF of B (128 of the
+ * 256 columns); the pair's tensor cores share the B halves, so per SM the MMAs read 96 KB,
+ * the split pass moves 64 KB and TMA writes 32 KB, and a stage is 64 KB, which makes room
+ * for three.  Loads carry no multicast: each CTA fetches its own tiles.
+ *
+ * Protocol (rank 0 of the cluster is the leader and issues every MMA):
+ *   full[s]    local : each CTA's TMA bytes for stage s (own A rows, own B half)
+ *   lo[s]      leader: 2 x 256 arrivals, the split threads of BOTH CTAs (remote arrive)
+ *   empty[s]   both  : tcgen05.commit multicast from the leader when the MMAs have read stage s
+ *   tfull[a]   both  : tcgen05.commit multicast when accumulator a is complete
+ *   tempty[a]  leader: 2 x 128 arrivals, the epilogue threads of both CTAs
+ * Every CTA runs its own producer, split and epilogue warps on its own half of the tile. */
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                  uint32_t *status, uint32_t code) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    long long t0 = clock64();
+    for (;;) {
+        #pragma unroll 1
+        for (int i = 0; i < 16; i++)
+            if (mbar_try_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TC_WAIT_CYCLES) {
+            *abort_flag = 1;
+            *(volatile uint32_t *)status = code | (blockIdx.x << 8);
+            __threadfence_system();
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc2_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int A_MN, int B_MN, int SPLIT_ACC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+    constexpr int BK = 32, STAGES = 3;
+    constexpr int BN = 256, BNH = 128;                       /* pair tile is 256 wide, each CTA stages 128 columns of B */
+    constexpr uint32_t A_BYTES = TC_BM * BK * 4;              /* 16 KB: this CTA's 128 rows */
+    constexpr uint32_t B_BYTES = BNH * BK * 4;                /* 16 KB: this CTA's half of B */
+    constexpr uint32_t BOX = BK * 128;
+    constexpr uint32_t HI_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t STAGE_BYTES = 2 * HI_BYTES;
+    /* M = 256 across the pair, N = 256 */
+    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)A_MN << 15) |
+                               ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr int NACC = SPLIT_ACC ? 1 : 2;
+    constexpr int TC_PREFETCH = STAGES + 4;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t *bars = (uint64_t *)(smem_gen + STAGES * STAGE_BYTES);
+    const uint32_t bar_full = smem_u32(bars);
+    const uint32_t bar_lo = bar_full + 8 * STAGES;
+    const uint32_t bar_empty = bar_lo + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 4);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_m = (p.M + 255) / 256;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int num_items = num_tiles * p.splits;
+    auto decode = [&](int it, int &m0, int &n0, int &kb0, int &kb1, int &split) {
+        split = it / num_tiles;
+        const int t = it - split * num_tiles;
+        m0 = (t % tiles_m) * 256; n0 = (t / tiles_m) * BN;
+        kb0 = split * p.kb_per_split;
+        kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_lo + 8 * s, 2 * TC_SPLIT_THREADS);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 2 * TC_EPI_THREADS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                       /* both CTAs' barriers exist before anybody signals across */
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    /* the leader's copies of the barriers everybody arrives on */
+    const uint32_t lead_lo = map_to_cta(bar_lo, 0);
+    const uint32_t lead_tempty = map_to_cta(bar_tempty, 0);
+
+    if (warp == 0) {
+        /* ---------------- TMA producer: own A rows, own half of B ---------------- */
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            bool ok = true;
+            auto coords = [&](int m0, int n0, int &ma, int &nb) { ma = m0 + (int)rank * TC_BM; nb = n0 + (int)rank * BNH; };
+            auto prefetch = [&](int m0, int n0, int kb) {
+                int ma, nb; coords(m0, n0, ma, nb);
+                const int k0 = kb * BK;
+                if (A_MN && p.a_3d) tma_prefetch_3d(&map_a, 0, k0, ma / 32);
+                else if (A_MN) { for (int b = 0; b < TC_BM / 32; b++) tma_prefetch_2d(&map_a, ma + 32 * b, k0); }
+                else tma_prefetch_2d(&map_a, k0, ma);
+                if (B_MN && p.b_3d) tma_prefetch_3d(&map_b, 0, k0, nb / 32);
+                else if (B_MN) { for (int b = 0; b < BNH / 32; b++) tma_prefetch_2d(&map_b, nb + 32 * b, k0); }
+                else tma_prefetch_2d(&map_b, k0, nb);
+            };
+            for (int it = pair; it < num_items && ok; it += num_pairs) {
+                int m0, n0, kb0, kb1, split;
+                decode(it, m0, n0, kb0, kb1, split);
+                int ma, nb; coords(m0, n0, ma, nb);
+                if (it == pair)
+                    for (int kb = kb0 + STAGES; kb < kb0 + TC_PREFETCH && kb < kb1; kb++) prefetch(m0, n0, kb);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    const int pk = kb + TC_PREFETCH;
+                    if (pk < kb1) {
+                        prefetch(m0, n0, pk);
+                    } else if (it + num_pairs < num_items) {
+                        int m2, n2, kb2, kb3, s2;
+                        decode(it + num_pairs, m2, n2, kb2, kb3, s2);
+                        if (kb2 + (pk - kb1) < kb3) prefetch(m2, n2, kb2 + (pk - kb1));
+                    }
+                    if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
+                    const uint32_t st = smem_base + s * STAGE_BYTES;
+                    const uint32_t full = bar_full + 8 * s;
+                    const int k0 = kb * BK;
+                    mbar_expect_tx(full, HI_BYTES);
+                    if (A_MN && p.a_3d) tma_load_3d(st, &map_a, full, 0, k0, ma / 32);
+                    else if (A_MN) { for (int b = 0; b < TC_BM / 32; b++) tma_load_2d(st + b * BOX, &map_a, full, ma + 32 * b, k0); }
+                    else tma_load_2d(st, &map_a, full, k0, ma);
+                    if (B_MN && p.b_3d) tma_load_3d(st + A_BYTES, &map_b, full, 0, k0, nb / 32);
+                    else if (B_MN) { for (int b = 0; b < BNH / 32; b++) tma_load_2d(st + A_BYTES + b * BOX, &map_b, full, nb + 32 * b, k0); }
+                    else tma_load_2d(st + A_BYTES, &map_b, full, k0, nb);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+            if (!ok) { long long t0 = clock64(); while (clock64() - t0 < 200000) { } }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issuer: the leader CTA only ---------------- */
+        if (lane == 0 && rank == 0) {
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int it = pair; it < num_items && ok; it += num_pairs) {
+                int m0, n0, kb0, kb1, split;
+                decode(it, m0, n0, kb0, kb1, split);
+                if (!mbar_wait_cluster(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 4)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_main = tmem_base + (uint32_t)(SPLIT_ACC ? 0 : acc * BN);
+                const uint32_t d_corr = SPLIT_ACC ? tmem_base + (uint32_t)BN : d_main;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait_cluster(bar_lo + 8 * s, ph, abort_flag, p.status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_hi = smem_base + s * STAGE_BYTES;
+                    const uint32_t b_hi = a_hi + A_BYTES;
+                    const uint32_t a_lo = a_hi + HI_BYTES;
+                    const uint32_t b_lo = b_hi + HI_BYTES;
+                    #pragma unroll
+                    for (int ks = 0; ks < BK / 8; ks++) {
+                        const uint32_t a_off = A_MN ? ks * 1024 : ks * 32;
+                        const uint32_t b_off = B_MN ? ks * 1024 : ks * 32;
+                        const uint64_t da_hi = make_desc<A_MN, BK>(a_hi + a_off);
+                        const uint64_t db_hi = make_desc<B_MN, BK>(b_hi + b_off);
+                        const uint32_t first = (kb > kb0 || ks > 0) ? 1u : 0u;
+                        if (p.passes == 3) {
+                            const uint64_t da_lo = make_desc<A_MN, BK>(a_lo + a_off);
+                            const uint64_t db_lo = make_desc<B_MN, BK>(b_lo + b_off);
+                            tc2_mma_tf32(d_corr, da_lo, db_hi, IDESC, first);
+                            tc2_mma_tf32(d_corr, da_hi, db_lo, IDESC, 1u);
+                            tc2_mma_tf32(d_main, da_hi, db_hi, IDESC, SPLIT_ACC ? first : 1u);
+                        } else {
+                            tc2_mma_tf32(d_main, da_hi, db_hi, IDESC, first);
+                        }
+                    }
+                    tc2_commit_both(bar_empty + 8 * s);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                tc2_commit_both(bar_tfull + 8 * acc);
+                if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+    } else if (warp < 2 + TC_SPLIT_THREADS / 32) {
+        /* ---------------- split warps: own tiles, report to the leader ---------------- */
+        const int st_tid = threadIdx.x - 64;
+        int s = 0; uint32_t ph = 0;
+        bool ok = true;
+        for (int it = pair; it < num_items && ok; it += num_pairs) {
+            int m0, n0, kb0, kb1, split;
+            decode(it, m0, n0, kb0, kb1, split);
+            for (int kb = kb0; kb < kb1; kb++) {
+                if (!mbar_wait_warp(bar_full + 8 * s, ph, abort_flag, p.status, 1)) { ok = false; break; }
+                if (p.passes == 3 && !p.nosplit) {
+                    const uint8_t *hi = smem_gen + s * STAGE_BYTES;
+                    #pragma unroll 4
+                    for (uint32_t c = st_tid; c < HI_BYTES / 16; c += TC_SPLIT_THREADS) {
+                        float4 v = *(const float4 *)(hi + c * 16);
+                        float4 w = make_float4(split_lo(v.x), split_lo(v.y), split_lo(v.z), split_lo(v.w));
+                        *(float4 *)(hi + HI_BYTES + c * 16) = w;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                mbar_arrive_cluster(lead_lo + 8 * s);
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+    } else {
+        /* ---------------- epilogue warps: this CTA's 128 rows, all 256 columns ---------------- */
+        const int q = warp & 3;
+        int acc = 0; uint32_t acc_ph = 0;
+        bool ok = true;
+        const bool sliced = p.splits > 1;
+        const long ldc = sliced ? (long)p.N : p.ldc;
+        const float *bias = sliced ? nullptr : p.bias;
+        const int accumulate = sliced ? 0 : p.accumulate;
+        for (int it = pair; it < num_items && ok; it += num_pairs) {
+            int m0, n0, kb0, kb1, split;
+            decode(it, m0, n0, kb0, kb1, split);
+            float *cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
+            const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0);
+            if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + (int)rank * TC_BM + q * 32 + lane;
+            float *crow = cbase + (long)row * ldc;
+            #pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                if (SPLIT_ACC && p.passes == 3) {
+                    uint32_t r2[32];
+                    tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), r2);
+                    tc_wait_ld();
+                    #pragma unroll
+                    for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                }
+                tc_wait_ld();
+                if (c0 + 32 >= BN) {
+                    tc_fence_before();
+                    mbar_arrive_cluster(lead_tempty + 8 * acc);
+                }
+                const int gc = n0 + c0;
+                if (row < p.M && gc < p.N) {
+                    if (vec_ok && gc + 32 <= p.N) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            if (bias) { v.x += bias[gc + j]; v.y += bias[gc + j + 1]; v.z += bias[gc + j + 2]; v.w += bias[gc + j + 3]; }
+                            if (accumulate) {
+                                float4 o = *(const float4 *)(crow + gc + j);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *(float4 *)(crow + gc + j) = v;
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (gc + j < p.N) {
+                                float v = __uint_as_float(r[j]);
+                                if (bias) v += bias[gc + j];
+                                if (accumulate) v += crow[gc + j];
+                                crow[gc + j] = v;
+                            }
+                        }
+                    }
+                }
+            }
+            if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                       /* no CTA leaves while its peer may still signal it or read its tiles */
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 /* Second phase of split-K: C[m,n] (+)= bias[n] + sum over slices, slices added in order. */
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, int splits, int M, int N,
                                                              float *__restrict__ C, long ldc, const float *__restrict__ bias,
@@ -504,6 +839,8 @@ static EncodeTiledFn g_encode = nullptr;
 static uint32_t *g_status_host = nullptr;     /* mapped pinned word the kernel reports into */
 static uint32_t *g_status_dev = nullptr;
 static int g_tc_passes = 3;
+static int g_tc_nosplit = 0;
+static int g_tc_2cta = 0;            /* TT_TC_2CTA=1: CTA-pair kernel for the big shapes */
 static int g_tc_force_bk = 0;        /* TT_TC_BK: tuning aid, 0 = by tile shape */
 static int g_tc_force_bn = 0;        /* TT_TC_BN: tuning aid, 0 = choose by tile count */
 static int g_tc_splitk = 1;          /* TT_TC_SPLITK=0: tuning aid, never cut the reduction across CTAs */
@@ -526,10 +863,14 @@ static int tc_setup(void) {
     if (!tt_cuda_ok(cudaHostGetDevicePointer((void **)&g_status_dev, g_status_host, 0), "cudaHostGetDevicePointer")) return -1;
     const char *e = getenv("TT_TC_PASSES");
     if (e && atoi(e) == 1) g_tc_passes = 1;
+    e = getenv("TT_TC_NOSPLIT");
+    if (e && atoi(e) == 1) g_tc_nosplit = 1;
     e = getenv("TT_TC_SPLITK");
     if (e && *e) g_tc_splitk = atoi(e);
     e = getenv("TT_TC_MN3D");
     if (e && *e) g_tc_mn3d = atoi(e);
+    e = getenv("TT_TC_2CTA");
+    if (e && *e) g_tc_2cta = atoi(e);
     e = getenv("TT_TC_BK");
     if (e && *e) g_tc_force_bk = atoi(e);
     e = getenv("TT_TC_BN");
@@ -607,7 +948,7 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     }
     TcParams p;
     p.M = g->M; p.N = g->N; p.K = g->K; p.C = g->C; p.ldc = g->ldc; p.bias = g->bias;
-    p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev;
+    p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev; p.nosplit = g_tc_nosplit;
     p.a_3d = a_3d; p.b_3d = b_3d;
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
     int tiles = ((g->M + TC_BM - 1) / TC_BM) * ((g->N + BN - 1) / BN) * p.splits;
@@ -626,6 +967,51 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     return tt_cuda_ok(cudaGetLastError(), "tcgen05 GEMM launch") ? 0 : -1;
 }
 
+template <int A_MN, int B_MN, int SPLIT_ACC>
+static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
+    constexpr size_t smem = (size_t)3 * 2 * (TC_BM * 32 * 4 + 128 * 32 * 4) + 1024 + 8 * (3 * 3 + 4) + 16;
+    static bool configured = false;
+    auto kern = gemm_tc2_kernel<A_MN, B_MN, SPLIT_ACC>;
+    if (!configured) {
+        if (!tt_cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                        "cudaFuncSetAttribute(smem)")) return -1;
+        configured = true;
+    }
+    TcParams p;
+    p.M = g->M; p.N = g->N; p.K = g->K; p.C = g->C; p.ldc = g->ldc; p.bias = g->bias;
+    p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev; p.nosplit = g_tc_nosplit;
+    p.a_3d = a_3d; p.b_3d = b_3d;
+    p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
+    long items = (long)((g->M + 255) / 256) * ((g->N + 255) / 256) * p.splits;
+    long pairs = g_tt.gemm_sms / 2;
+    if (items < pairs) pairs = items;
+    tt_trace_begin(TTB_K_GEMM_TC);
+    kern<<<(int)(2 * pairs), TC_THREADS, smem, g_tt.stream>>>(ma, mb, p);
+    g_tt.launches++;
+    if (p.splits > 1) {
+        long total = (long)g->M * g->N;
+        long blocks = (total + 255) / 256, cap = (long)g_tt.sm_count * 8;
+        splitk_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
+            p.partial, p.splits, g->M, g->N, g->C, g->ldc, g->bias, g->accumulate);
+        g_tt.launches++;
+    }
+    tt_trace_end(TTB_K_GEMM_TC, 2.0 * (double)g->M * g->N * g->K);
+    return tt_cuda_ok(cudaGetLastError(), "tcgen05 pair GEMM launch") ? 0 : -1;
+}
+static int launch_tc2(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d, bool split_acc) {
+    const int a_mn = g->ta ? 1 : 0, b_mn = g->tb ? 0 : 1;
+    if (split_acc) {
+        if (!a_mn && !b_mn) return launch_tc2_inst<0, 0, 1>(g, ma, mb, a_3d, b_3d);
+        if (!a_mn && b_mn)  return launch_tc2_inst<0, 1, 1>(g, ma, mb, a_3d, b_3d);
+        if (a_mn && !b_mn)  return launch_tc2_inst<1, 0, 1>(g, ma, mb, a_3d, b_3d);
+        return launch_tc2_inst<1, 1, 1>(g, ma, mb, a_3d, b_3d);
+    }
+    if (!a_mn && !b_mn) return launch_tc2_inst<0, 0, 0>(g, ma, mb, a_3d, b_3d);
+    if (!a_mn && b_mn)  return launch_tc2_inst<0, 1, 0>(g, ma, mb, a_3d, b_3d);
+    if (a_mn && !b_mn)  return launch_tc2_inst<1, 0, 0>(g, ma, mb, a_3d, b_3d);
+    return launch_tc2_inst<1, 1, 0>(g, ma, mb, a_3d, b_3d);
+}
+
 template <int BN, int BK, int STAGES, int SPLIT_ACC>
 static int launch_tc_major(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
     const int a_mn = g->ta ? 1 : 0, b_mn = g->tb ? 0 : 1;
@@ -642,37 +1028,41 @@ int gemm_tc(const GemmArgs *g) {
     const long tiles256 = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + 255) / 256);
     int bn = (tiles256 * 10 < (long)g_tt.gemm_sms * 7 || g->N <= 128) ? 128 : 256;
     if (g_tc_force_bn == 128 || g_tc_force_bn == 256) bn = g_tc_force_bn;
+    /* CTA pairs (256x256 tile over two SMs) for the big shapes */
+    const bool pair = g_tc_2cta && bn == 256 && g->M >= 256 && (g_tt.gemm_sms >= 2);
     CUtensorMap ma, mb;
     /* K blocks of 32 (two stages for 128x256 tiles, three for 128x128).  TT_TC_BK=16 selects 64-byte
      * rows with twice the stages; measured equal (the kernel is bound by shared-memory bandwidth,
      * not by pipeline depth), so it stays a tuning aid. */
     int bk = 32;
-    if (g_tc_force_bk == 16 || g_tc_force_bk == 32) bk = g_tc_force_bk;
+    if (!pair && (g_tc_force_bk == 16 || g_tc_force_bk == 32)) bk = g_tc_force_bk;
+    const int b_box = pair ? 128 : bn;                 /* in a pair each CTA stages half of B's columns */
     int a_3d = 0, b_3d = 0;
     if (g->ta) {
         if (g_tc_mn3d && g->M % 32 == 0 && encode_map_mn3d(&ma, g->A, g->M, g->K, g->lda, TC_BM / 32, bk) == 0) a_3d = 1;
         else if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, bk, 1)) return -1;
     } else if (encode_map(&ma, g->A, g->K, g->M, g->lda, bk, TC_BM, 0)) return -1;
     if (g->tb) {
-        if (encode_map(&mb, g->B, g->K, g->N, g->ldb, bk, bn, 0)) return -1;
-    } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, bn / 32, bk) == 0) b_3d = 1;
+        if (encode_map(&mb, g->B, g->K, g->N, g->ldb, bk, b_box, 0)) return -1;
+    } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, b_box / 32, bk) == 0) b_3d = 1;
     else if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, bk, 1)) return -1;
     /* Split-K when the tiles alone leave most SMs idle and the reduction is long enough to cut:
      * slices of at least four K blocks, as many as fill the machine, partials in pool scratch. */
     const int num_kb = (g->K + bk - 1) / bk;
-    const long tiles = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + bn - 1) / bn);
+    const long tiles = (long)((g->M + (pair ? 255 : TC_BM - 1)) / (pair ? 256 : TC_BM)) * ((g->N + bn - 1) / bn);
+    const int units = pair ? g_tt.gemm_sms / 2 : g_tt.gemm_sms;      /* CTAs, or CTA pairs, that take tiles */
     g_plan.splits = 1; g_plan.kb_per_split = num_kb; g_plan.partial = nullptr;
     long want = 1;
-    if (g_tc_splitk && tiles * 2 <= g_tt.gemm_sms && num_kb >= 2 * (128 / bk)) {
+    if (g_tc_splitk && tiles * 2 <= units && num_kb >= 2 * (128 / bk)) {
         /* few tiles: as many slices as fill the machine */
-        want = g_tt.gemm_sms / tiles;
+        want = units / tiles;
         if (want > num_kb / (128 / bk)) want = num_kb / (128 / bk);      /* slices of at least 128 along K */
     } else if (g_tc_splitk && (long)num_kb * bk >= 1024) {
         /* many tiles: the last wave may be mostly empty (512 tiles on 148 SMs run as 4 waves of
          * work worth 3.46).  Two to four slices change the wave count; take the cut whose gain
          * in occupancy outweighs writing and re-reading the partial products. */
-        const double sms = (double)g_tt.gemm_sms;
-        const double mma_us = 6.0 * g->M * (double)g->N * g->K / (sms * 4096.0 * 1.8e3 * 0.75);   /* microseconds at 75 % of the pipe */
+        const double sms = (double)units;
+        const double mma_us = 6.0 * g->M * (double)g->N * g->K / ((double)g_tt.gemm_sms * 4096.0 * 1.8e3 * 0.75);   /* microseconds at 75 % of the pipe */
         double best = 1e30;
         for (long sp = 1; sp <= 4; sp++) {
             if ((long)(num_kb / sp) * bk < 512) break;
@@ -698,7 +1088,8 @@ int gemm_tc(const GemmArgs *g) {
     /* long reductions keep the cross terms in their own accumulator (see the kernel) */
     const bool split_acc = (long)g_plan.kb_per_split * bk > g_tc_split_k;
     int rc;
-    if (bn == 256 && bk == 16) rc = split_acc ? launch_tc_major<256, 16, 4, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 16, 4, 0>(g, ma, mb, a_3d, b_3d);
+    if (pair) rc = launch_tc2(g, ma, mb, a_3d, b_3d, split_acc);
+    else if (bn == 256 && bk == 16) rc = split_acc ? launch_tc_major<256, 16, 4, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 16, 4, 0>(g, ma, mb, a_3d, b_3d);
     else if (bn == 256)        rc = split_acc ? launch_tc_major<256, 32, 2, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 32, 2, 0>(g, ma, mb, a_3d, b_3d);
     else if (bk == 16)         rc = split_acc ? launch_tc_major<128, 16, 6, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 16, 6, 0>(g, ma, mb, a_3d, b_3d);
     else                       rc = split_acc ? launch_tc_major<128, 32, 3, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 32, 3, 0>(g, ma, mb, a_3d, b_3d);
