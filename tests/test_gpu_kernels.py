@@ -181,7 +181,10 @@ def test_fused_softmax_xent_matches_the_composite(tt, orc):
 
 GEOMS = [(2, 2, 5, 5, 3, 3, 1, 1, 1, 1), (2, 3, 8, 7, 3, 2, 2, 1, 0, 1), (1, 1, 6, 6, 1, 1, 1, 1, 0, 0),
          (3, 4, 9, 9, 5, 5, 2, 2, 2, 2), (4, 3, 32, 32, 3, 3, 1, 1, 1, 1), (2, 32, 16, 16, 3, 3, 1, 1, 1, 1),
-         (1, 2, 7, 5, 2, 3, 3, 1, 4, 0)]
+         (1, 2, 7, 5, 2, 3, 3, 1, 4, 0),
+         # 3x3 / stride 1 / pad 1 with W in {4, 8, 128}: the shuffle kernels, rows that end inside a warp
+         (2, 3, 5, 4, 3, 3, 1, 1, 1, 1), (3, 5, 7, 8, 3, 3, 1, 1, 1, 1), (1, 2, 3, 128, 3, 3, 1, 1, 1, 1),
+         (1, 1, 9, 12, 3, 3, 1, 1, 1, 1)]
 
 
 @pytest.mark.parametrize("geom", GEOMS)
@@ -202,7 +205,7 @@ def test_im2col_col2im_bit_exact(tt, orc, geom):
 
 
 POOLS = [(2, 2, 6, 6, 2, 2, 2, 2), (2, 3, 7, 9, 3, 2, 1, 2), (1, 2, 5, 5, 3, 3, 1, 1), (2, 2, 8, 8, 2, 2, 3, 3),
-         (8, 32, 32, 32, 2, 2, 2, 2), (1, 1, 4, 4, 4, 4, 1, 1)]
+         (8, 32, 32, 32, 2, 2, 2, 2), (1, 1, 4, 4, 4, 4, 1, 1), (3, 5, 10, 12, 2, 2, 2, 2)]
 
 
 @pytest.mark.parametrize("geom", POOLS)

@@ -9,6 +9,8 @@
  * operators.  Each kernel names the reference loop it replaces. */
 #include "tt_internal.h"
 
+#include <stdlib.h>
+
 #include <math.h>
 
 #define TPB 256
@@ -297,7 +299,7 @@ __device__ __forceinline__ void softmax_row(const float *__restrict__ xr, int N,
     if (in_regs) {
         #pragma unroll
         for (int i = 0; i < SM_REG; i++) {
-            v[i] = sm_index(i, lane, vec) < N ? expf(v[i] - mx) : 0.0f;
+            v[i] = expf(v[i] - mx);          /* slots past the row hold -Inf and become 0 */
             sum += v[i];
         }
     } else {
@@ -340,7 +342,10 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_kernel(float *__restric
             continue;
         }
         if (in_regs) {
-            sm_store(orow, N, lane, v, vec, [sum](float e, int) { return e / sum; });
+            /* one division per row, then a multiply per element: within 1.5 ulp of e / sum, and the
+             * kernel stays under the time the row's bytes take (a per-element division does not) */
+            const float inv = 1.0f / sum;
+            sm_store(orow, N, lane, v, vec, [inv](float e, int) { return e * inv; });
         } else {
             for (int j = lane; j < N; j += 32) orow[j] = expf(xr[j] - mx) / sum;
         }
@@ -382,7 +387,7 @@ void k_softmax_bwd(float *dx, const float *s, const float *g, long rows, int N) 
  * followed by the NumPy lines of tests/gate_mnist_mlp.py:112-119:
  *   p = softmax(z); loss_r = -log(max(p[y_r], 1e-12)); dz = (p - onehot) * scale.
  * One pass over the logits, one write of dz, 4 bytes of loss per row. */
-__global__ void __launch_bounds__(SM_WARPS * 32) softmax_xent_kernel(const float *__restrict__ z, const float *__restrict__ labels,
+__global__ void __launch_bounds__(SM_WARPS * 32, 3) softmax_xent_kernel(const float *__restrict__ z, const float *__restrict__ labels,
                                                                        long rows, int N, float scale,
                                                                        float *__restrict__ dz, float *__restrict__ row_loss) {
     int lane = threadIdx.x & 31;
@@ -402,19 +407,26 @@ __global__ void __launch_bounds__(SM_WARPS * 32) softmax_xent_kernel(const float
             for (int j = lane; j < N; j += 32) drow[j] = (u - (j == y ? 1.0f : 0.0f)) * scale;
             py = u;
         } else {
-            float mine = 0.0f;
             if (in_regs) {
-                #pragma unroll
-                for (int i = 0; i < SM_REG; i++) if (sm_index(i, lane, vec) == y) mine = v[i] / sum;
-                sm_store(drow, N, lane, v, vec, [sum, scale, y](float e, int j) { return (e / sum - (j == y ? 1.0f : 0.0f)) * scale; });
+                /* the label's probability: every lane recomputes it from the (cached) logit with the
+                 * operations the stored row uses, so it equals the stored value plus the one-hot */
+                const float inv = 1.0f / sum;
+                const bool y_ok = y >= 0 && y < N;
+                py = y_ok ? expf(zr[y] - mx) * inv : 0.0f;
+                /* the row goes out as p * scale; the one element that carries the one-hot is then
+                 * rewritten by lane 0 (ordered after the row's stores by the warp barrier) */
+                sm_store(drow, N, lane, v, vec, [inv, scale](float e, int) { return (e * inv) * scale; });
+                __syncwarp();
+                if (lane == 0 && y_ok) drow[y] = (py - 1.0f) * scale;
             } else {
+                float mine = 0.0f;
                 for (int j = lane; j < N; j += 32) {
                     float p = expf(zr[j] - mx) / sum;
                     if (j == y) mine = p;
                     drow[j] = (p - (j == y ? 1.0f : 0.0f)) * scale;
                 }
+                py = warp_sum(mine);
             }
-            py = warp_sum(mine);
         }
         if (lane == 0) row_loss[row] = -logf(fmaxf(py, 1e-12f));
     }
@@ -514,21 +526,127 @@ __global__ void __launch_bounds__(TPB) colsum_final_kernel(const float *__restri
     for (int k = 0; k < slabs; k++) s += part[(long)k * N + n];
     out[n] = accumulate ? out[n] + s : s;
 }
+/* One-launch form for the pooled path: the block that finishes last among the row slabs of a
+ * column block (a ticket counter per column block, reset by its last user) adds the partial
+ * rows -- slab k goes to row lane k % 8, the eight lanes are then added in order, so the sum
+ * has one fixed shape whatever the arrival order -- and writes the result.  Saves the second
+ * launch, which for a 134 MB gradient is a fifth of the time. */
+#define CS_MAX_COL_BLOCKS 2048
+static __device__ unsigned int g_colsum_tickets[CS_MAX_COL_BLOCKS];
+/* CT threads across (four columns each), RT row lanes; CT * RT = 256 */
+template <int CT, int RT>
+__global__ void __launch_bounds__(256) colsum_fused_kernel(const float *__restrict__ g, int M, int N, int ldg,
+                                                                               int rows_per_slab, float *__restrict__ part,
+                                                                               float *__restrict__ out, int accumulate) {
+    __shared__ float4 sh[RT][CT];
+    __shared__ unsigned int ticket;
+    const int cx = threadIdx.x % CT, ry = threadIdx.x / CT;
+    const int col = blockIdx.x * (CT * 4) + cx * 4;
+    const int r0 = blockIdx.y * rows_per_slab;
+    const int r1 = r0 + rows_per_slab < M ? r0 + rows_per_slab : M;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool vec = ((ldg & 3) == 0) && ((((uintptr_t)g) & 15u) == 0) && (col + 3 < N);
+    int r = r0 + ry;
+    if (vec) {
+        for (; r + 3 * RT < r1; r += 4 * RT) {
+            const float *row = g + (long)r * ldg + col;
+            float4 a = *(const float4 *)row, b = *(const float4 *)(row + (long)RT * ldg);
+            float4 c = *(const float4 *)(row + 2l * RT * ldg), d = *(const float4 *)(row + 3l * RT * ldg);
+            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+            acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+            acc.x += c.x; acc.y += c.y; acc.z += c.z; acc.w += c.w;
+            acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+        }
+    }
+    for (; r < r1; r += RT) {
+        const float *row = g + (long)r * ldg;
+        if (vec) {
+            float4 v = *(const float4 *)(row + col);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        } else {
+            if (col < N) acc.x += row[col];
+            if (col + 1 < N) acc.y += row[col + 1];
+            if (col + 2 < N) acc.z += row[col + 2];
+            if (col + 3 < N) acc.w += row[col + 3];
+        }
+    }
+    sh[ry][cx] = acc;
+    __syncthreads();
+    /* the partial rows are padded to whole column blocks, so every block stores four floats */
+    const int NP = gridDim.x * (CT * 4);
+    if (ry == 0) {
+        #pragma unroll
+        for (int k = 1; k < RT; k++) {
+            float4 v = sh[k][cx];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *(float4 *)(part + (long)blockIdx.y * NP + col) = acc;
+        __threadfence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) ticket = atomicAdd(&g_colsum_tickets[blockIdx.x], 1u);
+    __syncthreads();
+    if (ticket != gridDim.y - 1) return;
+    __threadfence();
+    const int slabs = gridDim.y;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = ry; k < slabs; k += RT) {
+        float4 v = __ldcg((const float4 *)(part + (long)k * NP + col));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    sh[ry][cx] = acc;
+    __syncthreads();
+    if (ry == 0) {
+        #pragma unroll
+        for (int k = 1; k < RT; k++) {
+            float4 v = sh[k][cx];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (col < N) out[col] = accumulate ? out[col] + acc.x : acc.x;
+        if (col + 1 < N) out[col + 1] = accumulate ? out[col + 1] + acc.y : acc.y;
+        if (col + 2 < N) out[col + 2] = accumulate ? out[col + 2] + acc.z : acc.z;
+        if (col + 3 < N) out[col + 3] = accumulate ? out[col + 3] + acc.w : acc.w;
+    }
+    if (threadIdx.x == 0) g_colsum_tickets[blockIdx.x] = 0;      /* ready for the next launch */
+}
 void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate) {
-    int slabs = (M + 63) / 64;
-    int max_slabs = (2 * g_tt.sm_count * 8) / ((N + CS_COLS - 1) / CS_COLS) + 1;
-    if (slabs > max_slabs) slabs = max_slabs;
+    /* as many row slabs as give every SM its full set of resident blocks exactly once: a second,
+     * nearly empty wave of blocks costs as much time as the first */
+    static int per_sm = 0;
+    if (!per_sm) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, colsum_fused_kernel<32, 8>, 256, 0) != cudaSuccess || per_sm < 1)
+            per_sm = 4;
+    }
+    const int cols_per_block = CS_COLS;      /* 512 bytes of a row per warp; 2 KB wide blocks measured slower */
+    const int col_blocks = (N + cols_per_block - 1) / cols_per_block;
+    int slabs = (g_tt.sm_count * per_sm) / col_blocks;
+    if (slabs > (M + 31) / 32) slabs = (M + 31) / 32;
     if (slabs < 1) slabs = 1;
     int rows_per_slab = (M + slabs - 1) / slabs;
     slabs = (M + rows_per_slab - 1) / rows_per_slab;
-    float *part = (float *)tt_dev_alloc(sizeof(float) * (size_t)slabs * N);
+    const bool fused = col_blocks <= CS_MAX_COL_BLOCKS;
+    const long part_cols = fused ? (long)col_blocks * cols_per_block : N;
+    /* the partial rows live in a buffer that is kept between calls (about 0.6 MB for 4096 columns):
+     * a stream-ordered allocation and release around a 20 microsecond kernel showed in its time */
+    static float *scratch = nullptr;
+    static size_t scratch_floats = 0;
+    const size_t need = (size_t)slabs * part_cols;
+    if (need > scratch_floats) {
+        if (scratch) tt_dev_free(scratch);
+        scratch = (float *)tt_dev_alloc(sizeof(float) * need);
+        scratch_floats = scratch ? need : 0;
+    }
+    float *part = scratch;
     if (!part) return;
     tt_trace_begin(TTB_K_REDUCE);
-    dim3 grid((N + CS_COLS - 1) / CS_COLS, slabs);
-    LAUNCH(colsum_partial_kernel, grid, CS_COLS * CS_ROWS / 4, 0, g, M, N, ldg, rows_per_slab, part);
-    LAUNCH(colsum_final_kernel, (N + TPB - 1) / TPB, TPB, 0, part, slabs, N, out, accumulate);
+    dim3 grid(col_blocks, slabs);
+    if (fused) {
+        LAUNCH((colsum_fused_kernel<32, 8>), grid, 256, 0, g, M, N, ldg, rows_per_slab, part, out, accumulate);
+    } else {
+        LAUNCH(colsum_partial_kernel, grid, CS_COLS * CS_ROWS / 4, 0, g, M, N, ldg, rows_per_slab, part);
+        LAUNCH(colsum_final_kernel, (N + TPB - 1) / TPB, TPB, 0, part, slabs, N, out, accumulate);
+    }
     tt_trace_end(TTB_K_REDUCE, 4.0 * (double)M * N);
-    tt_dev_free(part);
 }
 
 /* ---- column sums for callers that must not allocate ----------------------------
