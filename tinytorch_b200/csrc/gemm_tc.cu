@@ -190,6 +190,13 @@ struct TcParams {
      * in order.  splits == 1: the epilogue writes C itself. */
     int splits, kb_per_split;
     float *partial;
+    /* Tail split (one-CTA kernel, splits == 1): the first num_tiles - tail_tiles tiles fill whole
+     * waves of CTAs and run over the full reduction; each of the last tail_tiles tiles is cut into
+     * tail_splits slices of tail_kb K blocks, so that the last, partly filled wave becomes a
+     * full wave of shorter items.  Slice s of tail tile j writes a dense 128 x BN block at
+     * tail_partial + (s * tail_tiles + j) * 128 * BN; a second kernel adds the slices in order. */
+    int tail_tiles, tail_splits, tail_kb;
+    float *tail_partial;
     uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
 };
 
@@ -231,14 +238,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + BK - 1) / BK;
-    const int num_items = num_tiles * p.splits;          /* work items: (K slice, tile) */
+    const int full_tiles = num_tiles - p.tail_tiles;     /* tiles that run over the whole reduction */
+    const int num_items = p.tail_tiles ? full_tiles + p.tail_tiles * p.tail_splits
+                                       : num_tiles * p.splits;          /* work items: (K slice, tile) */
     /* item -> first row, first column, K-block range, slice */
     auto decode = [&](int it, int &m0, int &n0, int &kb0, int &kb1, int &split) {
-        split = it / num_tiles;
-        const int t = it - split * num_tiles;
+        int t;
+        if (p.tail_tiles) {
+            if (it < full_tiles) { t = it; split = 0; kb0 = 0; kb1 = num_kb; }
+            else {
+                const int j = it - full_tiles;
+                split = j / p.tail_tiles;
+                t = full_tiles + (j - split * p.tail_tiles);
+                kb0 = split * p.tail_kb;
+                kb1 = kb0 + p.tail_kb < num_kb ? kb0 + p.tail_kb : num_kb;
+            }
+        } else {
+            split = it / num_tiles;
+            t = it - split * num_tiles;
+            kb0 = split * p.kb_per_split;
+            kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
+        }
         m0 = (t % tiles_m) * TC_BM; n0 = (t / tiles_m) * BN;
-        kb0 = split * p.kb_per_split;
-        kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
     };
 
     if (threadIdx.x == 0) {
@@ -409,19 +430,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int q = warp & 3;                       /* tensor-memory lane quarter this warp may read */
         int acc = 0; uint32_t acc_ph = 0;
         bool ok = true;
-        const bool sliced = p.splits > 1;
-        const long ldc = sliced ? (long)p.N : p.ldc;
-        const float *bias = sliced ? nullptr : p.bias;
-        const int accumulate = sliced ? 0 : p.accumulate;
         for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
             int m0, n0, kb0, kb1, split;
             decode(it, m0, n0, kb0, kb1, split);
-            float *cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
+            const bool tail = p.tail_tiles && it >= full_tiles;
+            const bool sliced = tail || p.splits > 1;
+            const long ldc = tail ? (long)BN : (sliced ? (long)p.N : p.ldc);
+            const float *bias = sliced ? nullptr : p.bias;
+            const int accumulate = sliced ? 0 : p.accumulate;
+            const int row = m0 + q * 32 + lane;
+            float *cbase, *crow;                       /* crow[n] addresses column n of this thread's row */
+            if (tail) {
+                const int j = it - full_tiles - split * p.tail_tiles;
+                cbase = p.tail_partial + ((long)split * p.tail_tiles + j) * (TC_BM * BN);
+                crow = cbase + (long)(q * 32 + lane) * BN - n0;
+            } else {
+                cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
+                crow = cbase + (long)row * ldc;
+            }
             const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0);
             if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5)) { ok = false; break; }   /* tcgen05.ld needs the whole warp */
             tc_fence_after();
-            const int row = m0 + q * 32 + lane;
-            float *crow = cbase + (long)row * ldc;
             #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -831,6 +860,43 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
     }
 }
 
+/* Second phase of the tail split: for each tail tile, C (+)= bias + slices in order. */
+__global__ void __launch_bounds__(256) tail_reduce_kernel(const float *__restrict__ partial, int splits, int tail_tiles,
+                                                           int first_tile, int tiles_m, int BN, int M, int N,
+                                                           float *__restrict__ C, long ldc, const float *__restrict__ bias,
+                                                           int accumulate) {
+    const int tile4 = TC_BM * BN / 4, bn4 = BN / 4;
+    const long total4 = (long)tail_tiles * tile4;
+    const long stride = (long)gridDim.x * blockDim.x;
+    const bool vec_c = ((ldc & 3) == 0) && ((((uintptr_t)C) & 15u) == 0);
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
+        const int tj = (int)(i / tile4);
+        const int rem = (int)(i - (long)tj * tile4);
+        const int r = rem / bn4, c = (rem - r * bn4) * 4;
+        const int t = first_tile + tj;
+        const int m = (t % tiles_m) * TC_BM + r, n = (t / tiles_m) * BN + c;
+        if (m >= M || n >= N) continue;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < splits; k++) {
+            const float4 v = *(const float4 *)(partial + ((long)k * tail_tiles + tj) * (TC_BM * BN) + (long)rem * 4);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        float *cp = C + (long)m * ldc + n;
+        if (vec_c && n + 3 < N) {
+            if (bias) { s.x += bias[n]; s.y += bias[n + 1]; s.z += bias[n + 2]; s.w += bias[n + 3]; }
+            if (accumulate) { const float4 o = *(const float4 *)cp; s.x = o.x + s.x; s.y = o.y + s.y; s.z = o.z + s.z; s.w = o.w + s.w; }
+            *(float4 *)cp = s;
+        } else {
+            const float sv[4] = {s.x, s.y, s.z, s.w};
+            for (int j = 0; j < 4 && n + j < N; j++) {
+                float v = sv[j];
+                if (bias) v += bias[n + j];
+                cp[j] = accumulate ? cp[j] + v : v;
+            }
+        }
+    }
+}
+
 /* ---- host side ----------------------------------------------------------------*/
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -844,6 +910,7 @@ static int g_tc_2cta = 0;            /* TT_TC_2CTA=1: CTA-pair kernel for the bi
 static int g_tc_force_bk = 0;        /* TT_TC_BK: tuning aid, 0 = by tile shape */
 static int g_tc_force_bn = 0;        /* TT_TC_BN: tuning aid, 0 = choose by tile count */
 static int g_tc_splitk = 1;          /* TT_TC_SPLITK=0: tuning aid, never cut the reduction across CTAs */
+static int g_tc_tail = 1;            /* TT_TC_TAIL=0: tuning aid, never cut only the last wave's tiles */
 static int g_tc_mn3d = 1;            /* TT_TC_MN3D=0: tuning aid, one TMA per 32 columns for MN-major tiles */
 static int g_tc_split_k = 1024;      /* reductions longer than this use the split accumulators */
 
@@ -867,6 +934,8 @@ static int tc_setup(void) {
     if (e && atoi(e) == 1) g_tc_nosplit = 1;
     e = getenv("TT_TC_SPLITK");
     if (e && *e) g_tc_splitk = atoi(e);
+    e = getenv("TT_TC_TAIL");
+    if (e && *e) g_tc_tail = atoi(e);
     e = getenv("TT_TC_MN3D");
     if (e && *e) g_tc_mn3d = atoi(e);
     e = getenv("TT_TC_2CTA");
@@ -934,7 +1003,7 @@ int gemm_tc_usable(const GemmArgs *g) {
 }
 
 /* Split-K plan of the launch being prepared (host side, single caller thread). */
-static struct { int splits, kb_per_split; float *partial; } g_plan = {1, 0, nullptr};
+static struct { int splits, kb_per_split; float *partial; int tail_tiles, tail_splits, tail_kb; float *tail_partial; } g_plan = {1, 0, nullptr, 0, 0, 0, nullptr};
 
 template <int A_MN, int B_MN, int BN, int BK, int STAGES, int SPLIT_ACC>
 static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
@@ -951,12 +1020,23 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev; p.nosplit = g_tc_nosplit;
     p.a_3d = a_3d; p.b_3d = b_3d;
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
-    int tiles = ((g->M + TC_BM - 1) / TC_BM) * ((g->N + BN - 1) / BN) * p.splits;
+    p.tail_tiles = g_plan.tail_tiles; p.tail_splits = g_plan.tail_splits; p.tail_kb = g_plan.tail_kb;
+    p.tail_partial = g_plan.tail_partial;
+    const int tiles_m = (g->M + TC_BM - 1) / TC_BM;
+    const int plain_tiles = tiles_m * ((g->N + BN - 1) / BN);
+    int tiles = p.tail_tiles ? plain_tiles - p.tail_tiles + p.tail_tiles * p.tail_splits : plain_tiles * p.splits;
     int grid = tiles < g_tt.gemm_sms ? tiles : g_tt.gemm_sms;
     tt_trace_begin(TTB_K_GEMM_TC);
     kern<<<grid, TC_THREADS, smem, g_tt.stream>>>(ma, mb, p);
     g_tt.launches++;
-    if (p.splits > 1) {
+    if (p.tail_tiles) {
+        long total4 = (long)p.tail_tiles * TC_BM * BN / 4;
+        long blocks = (total4 + 255) / 256, cap = (long)g_tt.sm_count * 8;
+        tail_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
+            p.tail_partial, p.tail_splits, p.tail_tiles, plain_tiles - p.tail_tiles, tiles_m, BN, g->M, g->N,
+            g->C, g->ldc, g->bias, g->accumulate);
+        g_tt.launches++;
+    } else if (p.splits > 1) {
         long total = (long)g->M * g->N;
         long blocks = (total + 255) / 256, cap = (long)g_tt.sm_count * 8;
         splitk_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
@@ -982,6 +1062,7 @@ static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUten
     p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev; p.nosplit = g_tc_nosplit;
     p.a_3d = a_3d; p.b_3d = b_3d;
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
+    p.tail_tiles = 0; p.tail_splits = 0; p.tail_kb = 0; p.tail_partial = nullptr;
     long items = (long)((g->M + 255) / 256) * ((g->N + 255) / 256) * p.splits;
     long pairs = g_tt.gemm_sms / 2;
     if (items < pairs) pairs = items;
@@ -1052,26 +1133,39 @@ int gemm_tc(const GemmArgs *g) {
     const long tiles = (long)((g->M + (pair ? 255 : TC_BM - 1)) / (pair ? 256 : TC_BM)) * ((g->N + bn - 1) / bn);
     const int units = pair ? g_tt.gemm_sms / 2 : g_tt.gemm_sms;      /* CTAs, or CTA pairs, that take tiles */
     g_plan.splits = 1; g_plan.kb_per_split = num_kb; g_plan.partial = nullptr;
+    g_plan.tail_tiles = 0; g_plan.tail_splits = 0; g_plan.tail_kb = 0; g_plan.tail_partial = nullptr;
     long want = 1;
+    long tail_s = 0;                                   /* > 1: cut only the tiles of the last wave */
     if (g_tc_splitk && tiles * 2 <= units && num_kb >= 2 * (128 / bk)) {
         /* few tiles: as many slices as fill the machine */
         want = units / tiles;
         if (want > num_kb / (128 / bk)) want = num_kb / (128 / bk);      /* slices of at least 128 along K */
     } else if (g_tc_splitk && (long)num_kb * bk >= 1024) {
         /* many tiles: the last wave may be mostly empty (512 tiles on 148 SMs run as 4 waves of
-         * work worth 3.46).  Two to four slices change the wave count; take the cut whose gain
-         * in occupancy outweighs writing and re-reading the partial products. */
+         * work worth 3.46).  Either every tile is cut into two to four slices, or only the
+         * tiles of the last wave are (the earlier waves are full already, and the partial
+         * products to write and re-read are a fraction).  Each candidate is priced as waves
+         * of MMA time plus the traffic of its partial products; the cheapest wins. */
         const double sms = (double)units;
-        const double mma_us = 6.0 * g->M * (double)g->N * g->K / ((double)g_tt.gemm_sms * 4096.0 * 1.8e3 * 0.75);   /* microseconds at 75 % of the pipe */
+        const double tile_us = 6.0 * (pair ? 256.0 : 128.0) * bn * (double)g->K / (4096.0 * 1.8e3 * 0.75);   /* one tile on one SM (pair), 75 % of the pipe */
         double best = 1e30;
         for (long sp = 1; sp <= 4; sp++) {
             if ((long)(num_kb / sp) * bk < 512) break;
             const double items = (double)tiles * sp;
             const double waves = (double)((long)((items + sms - 1) / sms));
-            const double eff = items / (waves * sms);
             const double extra_us = sp > 1 ? (2.0 * sp + 1.0) * g->M * (double)g->N * 4.0 / 5.0e6 + 6.0 : 0.0;
-            const double t = mma_us / eff + extra_us;
+            const double t = tile_us * waves / sp + extra_us;
             if (t < best * 0.98) { best = t; want = sp; }
+        }
+        const long full_waves = tiles / units, rest = tiles - full_waves * units;
+        if (!pair && g_tc_tail && full_waves >= 1 && rest > 0) {
+            for (long sp = 2; sp <= 8; sp++) {
+                if ((long)(num_kb / sp) * bk < 256) break;
+                const double waves = (double)((rest * sp + units - 1) / units);
+                const double extra_us = (2.0 * sp + 1.0) * rest * 128.0 * bn * 4.0 / 5.0e6 + 6.0;
+                const double t = tile_us * ((double)full_waves + waves / sp) + extra_us;
+                if (t < best * 0.98) { best = t; want = 1; tail_s = sp; }
+            }
         }
     }
     if (want >= 2) {
@@ -1084,6 +1178,13 @@ int gemm_tc(const GemmArgs *g) {
         float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * g->M * g->N);
         if (!scratch) return -1;
         g_plan.splits = splits; g_plan.kb_per_split = per; g_plan.partial = scratch;
+    } else if (tail_s >= 2) {
+        const long rest = tiles % units;
+        const int per = (int)((num_kb + tail_s - 1) / tail_s);
+        const int splits = (num_kb + per - 1) / per;
+        float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * rest * TC_BM * bn);
+        if (!scratch) return -1;
+        g_plan.tail_tiles = (int)rest; g_plan.tail_splits = splits; g_plan.tail_kb = per; g_plan.tail_partial = scratch;
     }
     /* long reductions keep the cross terms in their own accumulator (see the kernel) */
     const bool split_acc = (long)g_plan.kb_per_split * bk > g_tc_split_k;
@@ -1094,6 +1195,8 @@ int gemm_tc(const GemmArgs *g) {
     else if (bk == 16)         rc = split_acc ? launch_tc_major<128, 16, 6, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 16, 6, 0>(g, ma, mb, a_3d, b_3d);
     else                       rc = split_acc ? launch_tc_major<128, 32, 3, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<128, 32, 3, 0>(g, ma, mb, a_3d, b_3d);
     if (g_plan.partial) tt_dev_free(g_plan.partial);
+    if (g_plan.tail_partial) tt_dev_free(g_plan.tail_partial);
     g_plan.splits = 1; g_plan.partial = nullptr;
+    g_plan.tail_tiles = 0; g_plan.tail_partial = nullptr;
     return rc;
 }
