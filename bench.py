@@ -411,8 +411,12 @@ def run_kernels(args):
     T = ns.Tensor.from_np
     rows = []
 
+    small = bool(args.small)                      # a quarter of the rows / images, two launches each: the case a profiler captures
+    SM_ROWS = 32768 if small else 65536
+    B = 512 if small else 2048
+
     def add(name, nbytes, fn, cpu_fn=None, cpu_scale=1.0):
-        ms = _time_op(ns, fn)
+        ms = _time_op(ns, fn, reps=1, warm=1) if small else _time_op(ns, fn)
         gbs = nbytes / (ms * 1e-3) / 1e9
         row = {"kernel": name, "bytes": int(nbytes), "ms": ms, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm}
         if cpu_fn is not None and not args.no_cpu_baseline:
@@ -423,9 +427,9 @@ def run_kernels(args):
     # large MLP activations: [8192, 4096] = 134 MB
     x = rng.standard_normal((8192, 4096)).astype(np.float32); g = rng.standard_normal((8192, 4096)).astype(np.float32)
     xt, gt = T(x), T(g)
-    small = slice(0, 512)
-    add("relu [8192,4096]", 8 * x.size, lambda: [ns.Tensor(ns.LIB.tt_relu(xt.ptr))], lambda: O.relu(x[small]), 16)
-    add("relu_bwd [8192,4096]", 12 * x.size, lambda: [ns.relu_bwd(xt, gt)], lambda: O.relu_bwd(x[small], g[small]), 16)
+    part = slice(0, 512)
+    add("relu [8192,4096]", 8 * x.size, lambda: [ns.Tensor(ns.LIB.tt_relu(xt.ptr))], lambda: O.relu(x[part]), 16)
+    add("relu_bwd [8192,4096]", 12 * x.size, lambda: [ns.relu_bwd(xt, gt)], lambda: O.relu_bwd(x[part], g[part]), 16)
     add("colsum [8192,4096]", 4 * x.size, lambda: [ns.colsum(gt)])
     w = T(x[:4097]); gw = T(g[:4097])
     add("sgd [4097,4096]", 12 * 4097 * 4096, lambda: (ns.sgd_step(w, gw, 0.1), [])[1])
@@ -434,13 +438,12 @@ def run_kernels(args):
     # the spatial and softmax tensors of the configurations are 30-80 MB and take 10-20 us, less than the
     # host needs to enqueue the next launch; they are scaled up eightfold (same row and plane shapes, more
     # rows / images) so that the timing sees the kernel and not the launch path
-    z = rng.standard_normal((65536, 1000)).astype(np.float32); y = rng.integers(0, 1000, size=65536).astype(np.float32)
+    z = rng.standard_normal((SM_ROWS, 1000)).astype(np.float32); y = rng.integers(0, 1000, size=SM_ROWS).astype(np.float32)
     zt, yt = T(z), T(y)
-    add("softmax_xent [65536,1000]", 8 * z.size, lambda: list(ns.softmax_xent(zt, yt, 1.0 / 8192)), lambda: O.softmax(z[small]), 128)
-    add("softmax [65536,1000]", 8 * z.size, lambda: [ns.Tensor(ns.LIB.tt_softmax(zt.ptr))])
+    add(f"softmax_xent [{SM_ROWS},1000]", 8 * z.size, lambda: list(ns.softmax_xent(zt, yt, 1.0 / 8192)), lambda: O.softmax(z[part]), SM_ROWS / 512)
+    add(f"softmax [{SM_ROWS},1000]", 8 * z.size, lambda: [ns.Tensor(ns.LIB.tt_softmax(zt.ptr))])
     zt.release(); yt.release()
     # CNN tensors, 2048 images
-    B = 2048
     a1 = rng.standard_normal((B, 32, 32, 32)).astype(np.float32)              # conv1 output
     a1t = T(a1)
     g1 = rng.standard_normal((B, 32, 16, 16)).astype(np.float32); g1t = T(g1)
@@ -521,6 +524,8 @@ def main():
                     help="tuning aid: a smaller global batch reproduces the per-GPU shapes of a larger job on fewer GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
+    ap.add_argument("--small", action="store_true",
+                    help="kernels workload: a quarter of the rows and images, one warm-up and one timed launch each")
     ap.add_argument("--workload", choices=["mlp", "gemm", "kernels", "cnn"], default="mlp")
     ap.add_argument("--gemm-n", type=int, default=4096)
     args = ap.parse_args()

@@ -265,12 +265,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_lo + 8 * s, TC_SPLIT_THREADS);
+            mbar_init(bar_lo + 8 * s, TC_SPLIT_THREADS / 32);      /* one arrival per split warp */
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, TC_EPI_THREADS);
+            mbar_init(bar_tempty + 8 * a, TC_EPI_THREADS / 32);  /* one arrival per epilogue warp */
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -421,7 +421,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     /* make the generic-proxy writes visible to the tensor core's reads */
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                mbar_arrive(bar_lo + 8 * s);
+                /* every lane has fenced its own writes; the warp barrier orders them before the one arrival
+                 * (256 per-thread arrivals on one barrier word cost more shared-memory time than the split) */
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_lo + 8 * s);
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
@@ -466,7 +469,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (c0 + 32 >= BN) {
                     /* last read of this accumulator: hand it back before the stores */
                     tc_fence_before();
-                    mbar_arrive(bar_tempty + 8 * acc);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
                 }
                 const int gc = n0 + c0;
                 if (row < p.M && gc < p.N) {
@@ -523,10 +527,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
  *
  * Protocol (rank 0 of the cluster is the leader and issues every MMA):
  *   full[s]    local : each CTA's TMA bytes for stage s (own A rows, own B half)
- *   lo[s]      leader: 2 x 256 arrivals, the split threads of BOTH CTAs (remote arrive)
+ *   lo[s]      leader: 2 x 8 arrivals, one per split warp of BOTH CTAs (remote arrive)
  *   empty[s]   both  : tcgen05.commit multicast from the leader when the MMAs have read stage s
  *   tfull[a]   both  : tcgen05.commit multicast when accumulator a is complete
- *   tempty[a]  leader: 2 x 128 arrivals, the epilogue threads of both CTAs
+ *   tempty[a]  leader: 2 x 4 arrivals, one per epilogue warp of both CTAs
  * Every CTA runs its own producer, split and epilogue warps on its own half of the tile. */
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -618,24 +622,37 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + BK - 1) / BK;
-    const int num_items = num_tiles * p.splits;
+    const int full_tiles = num_tiles - p.tail_tiles;     /* see TcParams: only the last wave's tiles are cut along K */
+    const int num_items = p.tail_tiles ? full_tiles + p.tail_tiles * p.tail_splits : num_tiles * p.splits;
     auto decode = [&](int it, int &m0, int &n0, int &kb0, int &kb1, int &split) {
-        split = it / num_tiles;
-        const int t = it - split * num_tiles;
+        int t;
+        if (p.tail_tiles) {
+            if (it < full_tiles) { t = it; split = 0; kb0 = 0; kb1 = num_kb; }
+            else {
+                const int j = it - full_tiles;
+                split = j / p.tail_tiles;
+                t = full_tiles + (j - split * p.tail_tiles);
+                kb0 = split * p.tail_kb;
+                kb1 = kb0 + p.tail_kb < num_kb ? kb0 + p.tail_kb : num_kb;
+            }
+        } else {
+            split = it / num_tiles;
+            t = it - split * num_tiles;
+            kb0 = split * p.kb_per_split;
+            kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
+        }
         m0 = (t % tiles_m) * 256; n0 = (t / tiles_m) * BN;
-        kb0 = split * p.kb_per_split;
-        kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
     };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_lo + 8 * s, 2 * TC_SPLIT_THREADS);
+            mbar_init(bar_lo + 8 * s, 2 * TC_SPLIT_THREADS / 32);
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, 2 * TC_EPI_THREADS);
+            mbar_init(bar_tempty + 8 * a, 2 * TC_EPI_THREADS / 32);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -766,7 +783,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                mbar_arrive_cluster(lead_lo + 8 * s);
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(lead_lo + 8 * s);
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
@@ -775,19 +793,27 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int q = warp & 3;
         int acc = 0; uint32_t acc_ph = 0;
         bool ok = true;
-        const bool sliced = p.splits > 1;
-        const long ldc = sliced ? (long)p.N : p.ldc;
-        const float *bias = sliced ? nullptr : p.bias;
-        const int accumulate = sliced ? 0 : p.accumulate;
         for (int it = pair; it < num_items && ok; it += num_pairs) {
             int m0, n0, kb0, kb1, split;
             decode(it, m0, n0, kb0, kb1, split);
-            float *cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
+            const bool tail = p.tail_tiles && it >= full_tiles;
+            const bool sliced = tail || p.splits > 1;
+            const long ldc = tail ? (long)BN : (sliced ? (long)p.N : p.ldc);
+            const float *bias = sliced ? nullptr : p.bias;
+            const int accumulate = sliced ? 0 : p.accumulate;
+            const int row = m0 + (int)rank * TC_BM + q * 32 + lane;
+            float *cbase, *crow;                       /* crow[n] addresses column n of this thread's row */
+            if (tail) {
+                const int j = it - full_tiles - split * p.tail_tiles;
+                cbase = p.tail_partial + ((long)split * p.tail_tiles + j) * (256 * BN);
+                crow = cbase + (long)((int)rank * TC_BM + q * 32 + lane) * BN - n0;
+            } else {
+                cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
+                crow = cbase + (long)row * ldc;
+            }
             const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0);
             if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5)) { ok = false; break; }
             tc_fence_after();
-            const int row = m0 + (int)rank * TC_BM + q * 32 + lane;
-            float *crow = cbase + (long)row * ldc;
             #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -802,7 +828,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 tc_wait_ld();
                 if (c0 + 32 >= BN) {
                     tc_fence_before();
-                    mbar_arrive_cluster(lead_tempty + 8 * acc);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(lead_tempty + 8 * acc);
                 }
                 const int gc = n0 + c0;
                 if (row < p.M && gc < p.N) {
@@ -862,10 +889,10 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
 
 /* Second phase of the tail split: for each tail tile, C (+)= bias + slices in order. */
 __global__ void __launch_bounds__(256) tail_reduce_kernel(const float *__restrict__ partial, int splits, int tail_tiles,
-                                                           int first_tile, int tiles_m, int BN, int M, int N,
+                                                           int first_tile, int tiles_m, int BM, int BN, int M, int N,
                                                            float *__restrict__ C, long ldc, const float *__restrict__ bias,
                                                            int accumulate) {
-    const int tile4 = TC_BM * BN / 4, bn4 = BN / 4;
+    const int tile4 = BM * BN / 4, bn4 = BN / 4;
     const long total4 = (long)tail_tiles * tile4;
     const long stride = (long)gridDim.x * blockDim.x;
     const bool vec_c = ((ldc & 3) == 0) && ((((uintptr_t)C) & 15u) == 0);
@@ -874,11 +901,11 @@ __global__ void __launch_bounds__(256) tail_reduce_kernel(const float *__restric
         const int rem = (int)(i - (long)tj * tile4);
         const int r = rem / bn4, c = (rem - r * bn4) * 4;
         const int t = first_tile + tj;
-        const int m = (t % tiles_m) * TC_BM + r, n = (t / tiles_m) * BN + c;
+        const int m = (t % tiles_m) * BM + r, n = (t / tiles_m) * BN + c;
         if (m >= M || n >= N) continue;
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int k = 0; k < splits; k++) {
-            const float4 v = *(const float4 *)(partial + ((long)k * tail_tiles + tj) * (TC_BM * BN) + (long)rem * 4);
+            const float4 v = *(const float4 *)(partial + ((long)k * tail_tiles + tj) * ((long)BM * BN) + (long)rem * 4);
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
         float *cp = C + (long)m * ldc + n;
@@ -906,7 +933,7 @@ static uint32_t *g_status_host = nullptr;     /* mapped pinned word the kernel r
 static uint32_t *g_status_dev = nullptr;
 static int g_tc_passes = 3;
 static int g_tc_nosplit = 0;
-static int g_tc_2cta = 0;            /* TT_TC_2CTA=1: CTA-pair kernel for the big shapes */
+static int g_tc_2cta = 1;            /* TT_TC_2CTA=0: tuning aid, one-CTA kernel for every shape */
 static int g_tc_force_bk = 0;        /* TT_TC_BK: tuning aid, 0 = by tile shape */
 static int g_tc_force_bn = 0;        /* TT_TC_BN: tuning aid, 0 = choose by tile count */
 static int g_tc_splitk = 1;          /* TT_TC_SPLITK=0: tuning aid, never cut the reduction across CTAs */
@@ -1033,7 +1060,7 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
         long total4 = (long)p.tail_tiles * TC_BM * BN / 4;
         long blocks = (total4 + 255) / 256, cap = (long)g_tt.sm_count * 8;
         tail_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
-            p.tail_partial, p.tail_splits, p.tail_tiles, plain_tiles - p.tail_tiles, tiles_m, BN, g->M, g->N,
+            p.tail_partial, p.tail_splits, p.tail_tiles, plain_tiles - p.tail_tiles, tiles_m, TC_BM, BN, g->M, g->N,
             g->C, g->ldc, g->bias, g->accumulate);
         g_tt.launches++;
     } else if (p.splits > 1) {
@@ -1062,14 +1089,24 @@ static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUten
     p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev; p.nosplit = g_tc_nosplit;
     p.a_3d = a_3d; p.b_3d = b_3d;
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
-    p.tail_tiles = 0; p.tail_splits = 0; p.tail_kb = 0; p.tail_partial = nullptr;
-    long items = (long)((g->M + 255) / 256) * ((g->N + 255) / 256) * p.splits;
+    p.tail_tiles = g_plan.tail_tiles; p.tail_splits = g_plan.tail_splits; p.tail_kb = g_plan.tail_kb;
+    p.tail_partial = g_plan.tail_partial;
+    const int tiles_m = (g->M + 255) / 256;
+    const long plain_tiles = (long)tiles_m * ((g->N + 255) / 256);
+    long items = p.tail_tiles ? plain_tiles - p.tail_tiles + (long)p.tail_tiles * p.tail_splits : plain_tiles * p.splits;
     long pairs = g_tt.gemm_sms / 2;
     if (items < pairs) pairs = items;
     tt_trace_begin(TTB_K_GEMM_TC);
     kern<<<(int)(2 * pairs), TC_THREADS, smem, g_tt.stream>>>(ma, mb, p);
     g_tt.launches++;
-    if (p.splits > 1) {
+    if (p.tail_tiles) {
+        long total4 = (long)p.tail_tiles * 256 * 256 / 4;
+        long blocks = (total4 + 255) / 256, cap = (long)g_tt.sm_count * 8;
+        tail_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
+            p.tail_partial, p.tail_splits, p.tail_tiles, (int)plain_tiles - p.tail_tiles, tiles_m, 256, 256, g->M, g->N,
+            g->C, g->ldc, g->bias, g->accumulate);
+        g_tt.launches++;
+    } else if (p.splits > 1) {
         long total = (long)g->M * g->N;
         long blocks = (total + 255) / 256, cap = (long)g_tt.sm_count * 8;
         splitk_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
@@ -1158,11 +1195,11 @@ int gemm_tc(const GemmArgs *g) {
             if (t < best * 0.98) { best = t; want = sp; }
         }
         const long full_waves = tiles / units, rest = tiles - full_waves * units;
-        if (!pair && g_tc_tail && full_waves >= 1 && rest > 0) {
+        if (g_tc_tail && full_waves >= 1 && rest > 0) {
             for (long sp = 2; sp <= 8; sp++) {
                 if ((long)(num_kb / sp) * bk < 256) break;
                 const double waves = (double)((rest * sp + units - 1) / units);
-                const double extra_us = (2.0 * sp + 1.0) * rest * 128.0 * bn * 4.0 / 5.0e6 + 6.0;
+                const double extra_us = (2.0 * sp + 1.0) * rest * (pair ? 256.0 : 128.0) * bn * 4.0 / 5.0e6 + 6.0;
                 const double t = tile_us * ((double)full_waves + waves / sp) + extra_us;
                 if (t < best * 0.98) { best = t; want = 1; tail_s = sp; }
             }
@@ -1182,7 +1219,7 @@ int gemm_tc(const GemmArgs *g) {
         const long rest = tiles % units;
         const int per = (int)((num_kb + tail_s - 1) / tail_s);
         const int splits = (num_kb + per - 1) / per;
-        float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * rest * TC_BM * bn);
+        float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * rest * (pair ? 256 : TC_BM) * bn);
         if (!scratch) return -1;
         g_plan.tail_tiles = (int)rest; g_plan.tail_splits = splits; g_plan.tail_kb = per; g_plan.tail_partial = scratch;
     }
