@@ -324,7 +324,7 @@ def run_ours(args):
         "fwd_bwd_tflops_frac_of_tf32_peak": flops_step / (ms_step * 1e-3) / 1e12 / (tf32_peak * world),
         "final_loss": final_loss, "host_enqueue_ms_per_step": host_enqueue_ms,
         "roofline": {
-            "kernel": "gemm_tc_kernel (tcgen05.mma kind::tf32, 3xTF32 split, TMA-staged)",
+            "kernel": "gemm_tc2_kernel (tcgen05.mma.cta_group::2 kind::tf32 on CTA pairs, 3xTF32 split, TMA-staged)",
             "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
             "frac": achieved / tf32_peak if tf32_peak else None, "traffic": None,
             "launches": tc_n, "avg_launch_ms": tc_ms / tc_n if tc_n else None,
@@ -372,7 +372,11 @@ def run_gemm(args):
             "config": {"workload": f"isolated GEMM forward + backward, square {args.gemm_n}",
                        "l2": f"{res['operand_sets_per_pass']} independent operand sets per timed pass, more than L2 holds"},
             "roofline": {"bound": "tensor", "achieved": res["tflops"], "peak": peaks["bf16_tflops"] / 2.0, "unit": "TFLOP/s",
-                         "frac": res["frac_of_tf32_peak"], "traffic": None,
+                         "frac": res["frac_of_tf32_peak"],
+                         # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture of this
+                         # very case (square 4096); other sizes were not captured
+                         "traffic": 383.0e6 if args.gemm_n == 4096 else None,
+                         "algorithmic_bytes": 12.0 * args.gemm_n * args.gemm_n,
                          "peak_source": f"{peak_kind} bf16_tflops / 2 (burst: kernel timed alone)"},
             "gpu_launches": int(ns.LIB.ttb_launch_count())}
     print(json.dumps(line), flush=True)
