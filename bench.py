@@ -224,7 +224,9 @@ def run_ours(args):
     if ns.device_count() < 1:
         raise SystemExit("bench.py: no CUDA device visible; this library has no CPU path")
     ns.status(ns.LIB.ttb_init(local), "ttb_init")
-    D.connect(ns, rank, world)
+    # TT_DP_PEER=1: gradients go through the library's peer-memory all-reduce instead of ncclAllReduce
+    peer_floats = (DIMS[0] + 1) * DIMS[1] if os.environ.get("TT_DP_PEER", "0") == "1" else 0
+    D.connect(ns, rank, world, peer_floats=peer_floats)
     peaks, peak_kind = load_peaks()
     clocks = ClockSampler(local)
     if rank == 0:

@@ -168,6 +168,15 @@ void    ag_param_sgd(AGNode *leaf, float lr);
 int     ttb_dist_allreduce(Tensor *t);               /* sum over ranks, in place, async */
 int     ttb_dist_join(void);
 void    ttb_dist_finalize(void);
+/* Optional: reduce gradients with this library's own peer-memory kernel (plain NVLink loads and stores
+ * from CTAs that share SMs with the GEMM) instead of ncclAllReduce.  After ttb_dist_init every rank calls
+ * ttb_dist_peer_export (allocates its block for gradients of up to max_floats values, returns a 64-byte
+ * cudaIpc handle), the handles travel to all ranks by the same side channel as the NCCL id, and every
+ * rank calls ttb_dist_peer_import with the world x 64 bytes in rank order.  Gradients that are larger,
+ * not a multiple of four values or not 16-byte aligned still go through NCCL.  No reference counterpart. */
+int     ttb_dist_peer_export(size_t max_floats, int world, char handle_out[64]);
+int     ttb_dist_peer_import(int rank, int world, const char *handles);
+int     ttb_dist_peer_active(void);
 
 #ifdef __cplusplus
 }

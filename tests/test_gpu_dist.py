@@ -20,8 +20,25 @@ from oracle import oracle as O
 rank, world, local = D.init_process_group("gloo")
 ns = tinytorch_b200.default()
 ns.status(ns.LIB.ttb_init(local), "ttb_init")
-D.connect(ns, rank, world)
+peer_floats = int(sys.argv[2])
+D.connect(ns, rank, world, peer_floats=peer_floats)
 assert ns.LIB.ttb_dist_world() == world
+assert bool(ns.LIB.ttb_dist_peer_active()) == bool(peer_floats)
+# plain all-reduce of tensors every rank can regenerate: sizes that the peer kernel takes (a multiple
+# of four values, within the block), one beyond the block and one odd length (both fall back to NCCL)
+for n in (4, 1000, 262144 + 8, 2048 * 384, 3 * 2048 * 384, 1001):
+    parts = [np.random.default_rng(100 + r).standard_normal(n).astype(np.float32) for r in range(world)]
+    t = ns.Tensor.from_np(parts[rank])
+    for _ in range(2):                                   # twice: the second launch reuses the staging areas
+        ns.status(ns.LIB.ttb_dist_allreduce(t.ptr), "ttb_dist_allreduce")
+        ns.status(ns.LIB.ttb_dist_join(), "ttb_dist_join")
+    want = parts[0].copy()
+    for r in range(1, world):
+        want = want + parts[r]                           # rank order
+    once = t.to_np()
+    # after two reductions every rank holds world * (sum): check through the first one's algebra
+    assert np.array_equal(once, want * np.float32(world)), (n, np.abs(once - want * world).max())
+    t.release()
 rng = np.random.default_rng(5)
 dims, B = (2048, 384, 128, 40), 512      # first layer wide enough for the chunked dW + all-reduce path
 x = rng.standard_normal((B, dims[0])).astype(np.float32)
@@ -50,14 +67,17 @@ sys.stdout.write("rank%dok\n" % rank)
 """
 
 
-def test_two_gpu_data_parallel_matches_full_batch(tt, tmp_path):
+@pytest.mark.parametrize("peer_floats", [0, 2048 * 384 + 384], ids=["nccl", "peer-memory"])
+def test_two_gpu_data_parallel_matches_full_batch(tt, tmp_path, peer_floats):
+    """Once with every reduction through NCCL, once with the library's own peer-memory kernel for the
+    gradients that fit its block (the largest parameter of the model)."""
     if tt.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", "29633", str(script), ROOT]
+           "--master-addr", "127.0.0.1", "--master-port", "29633", str(script), ROOT, str(peer_floats)]
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert "rank0ok" in out.stdout and "rank1ok" in out.stdout

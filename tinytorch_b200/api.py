@@ -116,6 +116,9 @@ EXT_ABI = {
     "ttb_dist_allreduce": (CI, [VP]),
     "ttb_dist_join": (CI, []),
     "ttb_dist_finalize": (None, []),
+    "ttb_dist_peer_export": (CI, [ctypes.c_size_t, CI, ctypes.c_char_p]),
+    "ttb_dist_peer_import": (CI, [CI, CI, ctypes.c_char_p]),
+    "ttb_dist_peer_active": (CI, []),
 }
 
 # kernel classes of ttb_trace_read

@@ -12,7 +12,9 @@
  * NCCL is bound at run time with dlopen, so the library loads and the
  * single-GPU path works on a machine without NCCL, and a process that has
  * already loaded an NCCL (for instance through PyTorch) shares that copy
- * instead of pulling in a second one.  Failures are reported, never waited
+ * instead of pulling in a second one.  Gradients that fit the peer-memory
+ * block of peer_reduce.cu (when the ranks have exchanged its handles) are
+ * reduced by that kernel instead of ncclAllReduce.  Failures are reported, never waited
  * on: the communicator is created in blocking mode, every call's result is
  * checked, and ttb_dist_join polls ncclCommGetAsyncError. */
 #include "tt_internal.h"
@@ -122,8 +124,10 @@ int tt_dist_allreduce_async(Tensor *t) {
     if (!p) return -1;
     if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
         !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
-    if (!nccl_ok(nccl.AllReduce(p, p, (size_t)t->numel, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream),
-                 "ncclAllReduce")) return -1;
+    if (tt_peer_usable(p, (size_t)t->numel)) {
+        if (tt_peer_allreduce(p, (size_t)t->numel, g_tt.comm_stream) != 0) return -1;
+    } else if (!nccl_ok(nccl.AllReduce(p, p, (size_t)t->numel, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream),
+                        "ncclAllReduce")) return -1;
     g_inflight++;
     return 0;
 }
@@ -132,7 +136,9 @@ int tt_dist_allreduce_range(float *p, size_t count) {
     if (!tt_dist_active() || !count) return 0;
     if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
         !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
-    if (!nccl_ok(nccl.AllReduce(p, p, count, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream), "ncclAllReduce")) return -1;
+    if (tt_peer_usable(p, count)) {
+        if (tt_peer_allreduce(p, count, g_tt.comm_stream) != 0) return -1;
+    } else if (!nccl_ok(nccl.AllReduce(p, p, count, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream), "ncclAllReduce")) return -1;
     g_inflight++;
     return 0;
 }
@@ -151,6 +157,7 @@ extern "C" int ttb_dist_join(void) {
         g_inflight = 0;
     }
     if (!tt_dist_active()) return 0;
+    if (tt_peer_poll_status()) return -1;
     ncclResult_t async = 0;
     if (!nccl_ok(nccl.CommGetAsyncError(g_comm, &async), "ncclCommGetAsyncError")) return -1;
     if (async != 0 && async != 7) {
@@ -163,6 +170,7 @@ extern "C" int ttb_dist_join(void) {
 }
 
 extern "C" void ttb_dist_finalize(void) {
+    tt_peer_finalize();
     if (g_comm) {
         cudaStreamSynchronize(g_tt.comm_stream);
         nccl.CommDestroy(g_comm);

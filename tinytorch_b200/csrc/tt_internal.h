@@ -139,5 +139,10 @@ int gemm_tc_poll_status(void);                  /* non-zero (reason stored) when
 int tt_dist_active(void);
 int tt_dist_allreduce_async(Tensor *t);
 int tt_dist_allreduce_range(float *p, size_t count);     /* same, for a contiguous part of a gradient */
+/* peer-memory all-reduce (peer_reduce.cu) */
+int tt_peer_usable(const float *p, size_t count);
+int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream);
+int tt_peer_poll_status(void);
+void tt_peer_finalize(void);
 
 #endif

@@ -41,9 +41,14 @@ def init_process_group(backend="gloo"):
     return rank, world, local
 
 
-def connect(ns, rank, world):
+def connect(ns, rank, world, peer_floats=0):
     """Create the library's NCCL communicator: rank 0 makes the id, everybody
-    receives it through torch.distributed, everybody calls ttb_dist_init."""
+    receives it through torch.distributed, everybody calls ttb_dist_init.
+
+    peer_floats > 0 also sets up the library's own peer-memory all-reduce for
+    gradients of up to that many values: every rank exports its block, the
+    64-byte handles are gathered over torch.distributed, every rank opens the
+    others'.  Larger or oddly sized gradients keep going through NCCL."""
     import ctypes
     if world == 1:
         return
@@ -56,6 +61,14 @@ def connect(ns, rank, world):
     dist.broadcast(t, src=0)
     ident = bytes(t.tolist())
     ns.status(ns.LIB.ttb_dist_init(rank, world, ident), "ttb_dist_init")
+    if peer_floats:
+        handle = ctypes.create_string_buffer(64)
+        ns.status(ns.LIB.ttb_dist_peer_export(ctypes.c_size_t(int(peer_floats)), world, handle), "ttb_dist_peer_export")
+        mine = torch.tensor(list(handle.raw), dtype=torch.uint8)
+        everybody = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(everybody, mine)
+        blob = b"".join(bytes(t.tolist()) for t in everybody)
+        ns.status(ns.LIB.ttb_dist_peer_import(rank, world, blob), "ttb_dist_peer_import")
 
 
 def all_max(value):
