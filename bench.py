@@ -524,7 +524,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--ref-batch", type=int, default=256,
+    ap.add_argument("--ref-batch", type=int, default=1024,
                     help="samples per CPU step of the reference arm / CPU baseline (a slice of the global batch)")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="tuning aid: a smaller global batch reproduces the per-GPU shapes of a larger job on fewer GPUs")
