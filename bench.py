@@ -181,17 +181,27 @@ def workload_config(n_gpus):
 
 # ------------------------------------------------------------------ our arm
 def gemm_block(ns, peaks, cases=((1024, 5), (4096, 5))):
-    """Forward + backward GEMM throughput (C = A*B, dA = dC*B^T, dB = A^T*dC) on square
-    problems.  Each timed pass runs over enough independent operand sets that the pass as a
-    whole touches more than L2 holds (300 MB), back to back, so that small problems are
-    timed on the GPU and not on the host's launch path."""
+    """Forward + backward GEMM throughput (C = A*B, dA = dC*B^T, dB = A^T*dC).  A case is
+    (n, reps) for a square problem or ((M, K, N), reps).  Each timed pass runs over enough
+    independent operand sets that the pass as a whole touches more than L2 holds (300 MB),
+    back to back, so that small problems are timed on the GPU and not on the host's launch
+    path.  Every case is reported against both roofs: tensor (6MNK over the TF32 peak) and
+    HBM (12(MK+KN+MN) bytes, each operand read and each result written once per product,
+    over the measured copy bandwidth); `bound` names the one that allows less."""
     out = []
     tf32_peak = peaks["bf16_tflops"] / 2.0
-    for n, reps in cases:
-        sets = max(1, -(-300 * 1024 * 1024 // (3 * n * n * 4)))
+    hbm = peaks["hbm_gbs"]
+    for shape, reps in cases:
+        m, k, n = (shape, shape, shape) if isinstance(shape, int) else shape
+        bytes_alg = 12.0 * (m * k + k * n + m * n)
+        sets = max(1, -(-300 * 1024 * 1024 // int(bytes_alg / 3)))
+        sets = min(sets, 64)
         ops = []
         for i in range(sets):
-            a, b, dc = W.config_gemm(n, 1000 + i) if i else W.config_gemm(n, 1 if n == 1024 else 4)
+            if isinstance(shape, int):
+                a, b, dc = W.config_gemm(n, 1000 + i) if i else W.config_gemm(n, 1 if n == 1024 else 4)
+            else:
+                a, b, dc = W.config_gemm_shape(m, k, n, 4 + 1000 * i)
             ops.append((ns.Node.leaf(a, True), ns.Node.leaf(b, True), ns.Tensor.from_np(dc)))
         times = []
         for r in range(reps + 3):
@@ -207,9 +217,13 @@ def gemm_block(ns, peaks, cases=((1024, 5), (4096, 5))):
             if r >= 3:
                 times.append(ms)
         med = statistics.median(times)
-        tflops = 6.0 * n ** 3 / (med * 1e-3) / 1e12
-        out.append({"shape": [n, n, n], "ms": med, "operand_sets_per_pass": sets, "tflops": tflops,
-                    "frac_of_tf32_peak": tflops / tf32_peak, "tensor_pipe_frac_estimate": 3 * tflops / tf32_peak})
+        tflops = 6.0 * m * k * n / (med * 1e-3) / 1e12
+        gbs = bytes_alg / (med * 1e-3) / 1e9
+        t_tensor, t_hbm = 6.0 * m * k * n / (tf32_peak * 1e12), bytes_alg / (hbm * 1e9)
+        out.append({"shape": [m, k, n], "ms": med, "operand_sets_per_pass": sets, "tflops": tflops,
+                    "frac_of_tf32_peak": tflops / tf32_peak, "tensor_pipe_frac_estimate": 3 * tflops / tf32_peak,
+                    "algorithmic_gbs": gbs, "frac_of_hbm_peak": gbs / hbm,
+                    "bound": "hbm" if t_hbm > t_tensor else "tensor"})
         for an, bn, dct in ops:
             an.release(); bn.release(); dct.release()
     return out
@@ -367,19 +381,36 @@ def run_gemm(args):
     if ns.device_count() < 1:
         raise SystemExit("bench.py: no CUDA device visible; this library has no CPU path")
     peaks, peak_kind = load_peaks()
-    res = gemm_block(ns, peaks, cases=((args.gemm_n, max(args.steps, 1)),))[0]
+    if args.workload == "gemm-sweep":
+        # BASELINE.json configs[4]: every shape of the sweep, one line
+        rows = gemm_block(ns, peaks, cases=tuple(((m, k, n), 3) for m, k, n in W.GEMM_SWEEP))
+        line = {"metric": "gemm_fwd_bwd_tflops", "value": statistics.median([r["tflops"] for r in rows]), "unit": "TFLOP/s",
+                "n_gpus": 1, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "GEMM forward + backward shape sweep (BASELINE.json configs[4]); shapes are [M, K, N]",
+                           "l2": "independent operand sets per timed pass, more than L2 holds"},
+                "peak": {"tf32_tflops": peaks["bf16_tflops"] / 2.0, "hbm_gbs": peaks["hbm_gbs"], "source": peak_kind},
+                "shapes": rows, "gpu_launches": int(ns.LIB.ttb_launch_count())}
+        print(json.dumps(line), flush=True)
+        return
+    shape = tuple(int(v) for v in args.gemm_shape.split(",")) if args.gemm_shape else args.gemm_n
+    res = gemm_block(ns, peaks, cases=((shape, max(args.steps, 1)),))[0]
+    name = "x".join(map(str, res["shape"])) + " (M x K x N)"
+    hbm_bound = res["bound"] == "hbm"
     line = {"metric": "gemm_fwd_bwd_tflops", "value": res["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
             "steps": args.steps, "warmup": 3, "ms_per_step": res["ms"], "higher_is_better": True,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"isolated GEMM forward + backward, square {args.gemm_n}",
+            "config": {"workload": f"isolated GEMM forward + backward, {name}",
                        "l2": f"{res['operand_sets_per_pass']} independent operand sets per timed pass, more than L2 holds"},
-            "roofline": {"bound": "tensor", "achieved": res["tflops"], "peak": peaks["bf16_tflops"] / 2.0, "unit": "TFLOP/s",
-                         "frac": res["frac_of_tf32_peak"],
-                         # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture of this
-                         # very case (square 4096); other sizes were not captured
-                         "traffic": 383.0e6 if args.gemm_n == 4096 else None,
-                         "algorithmic_bytes": 12.0 * args.gemm_n * args.gemm_n,
-                         "peak_source": f"{peak_kind} bf16_tflops / 2 (burst: kernel timed alone)"},
+            "roofline": ({"bound": "hbm", "achieved": res["algorithmic_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                          "frac": res["frac_of_hbm_peak"], "traffic": None,
+                          "peak_source": f"{peak_kind} hbm_gbs (copy)"} if hbm_bound else
+                         {"bound": "tensor", "achieved": res["tflops"], "peak": peaks["bf16_tflops"] / 2.0, "unit": "TFLOP/s",
+                          "frac": res["frac_of_tf32_peak"],
+                          # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture of this
+                          # very case (square 4096); other sizes were not captured
+                          "traffic": 383.0e6 if res["shape"] == [4096, 4096, 4096] else None,
+                          "algorithmic_bytes": 4.0 * (res["shape"][0] * res["shape"][1] + res["shape"][1] * res["shape"][2] + res["shape"][0] * res["shape"][2]),
+                          "peak_source": f"{peak_kind} bf16_tflops / 2 (burst: kernel timed alone)"}),
             "gpu_launches": int(ns.LIB.ttb_launch_count())}
     print(json.dumps(line), flush=True)
 
@@ -532,7 +563,8 @@ def main():
     ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="kernels workload: a quarter of the rows and images, one warm-up and one timed launch each")
-    ap.add_argument("--workload", choices=["mlp", "gemm", "kernels", "cnn"], default="mlp")
+    ap.add_argument("--workload", choices=["mlp", "gemm", "gemm-sweep", "kernels", "cnn"], default="mlp")
+    ap.add_argument("--gemm-shape", default="", help="gemm workload: M,K,N instead of the square --gemm-n")
     ap.add_argument("--gemm-n", type=int, default=4096)
     args = ap.parse_args()
     GLOBAL_BATCH = args.global_batch
@@ -540,7 +572,7 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "gemm":
+    elif args.workload in ("gemm", "gemm-sweep"):
         run_gemm(args)
     elif args.workload == "kernels":
         run_kernels(args)

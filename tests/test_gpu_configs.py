@@ -70,6 +70,35 @@ def test_config2_gemm_1024_forward_backward(tt, golden_steps):
         assert np.array_equal(ex[k].reshape(-1)[idx], g[f"cfg2_{k}_val"]), k
 
 
+@pytest.mark.parametrize("shape", W.GEMM_SWEEP, ids=lambda s: "x".join(map(str, s)))
+def test_config5_gemm_shape_sweep(tt, shape):
+    """Every shape of the sweep, forward and both backward products through the autograd path.
+    Up to 2 GFLOP per product the three results are compared with float64 products in full; above
+    that through properties that cost O(MK + KN + MN) in float64 -- row and column sums of each
+    product -- plus a few hundred entries recomputed exactly."""
+    m, k, n = shape
+    a, b, dc = W.config_gemm_shape(m, k, n)
+    got = W.gemm_fwd_bwd(tt, a, b, dc)
+    a64, b64, d64 = a.astype(np.float64), b.astype(np.float64), dc.astype(np.float64)
+    if 2.0 * m * k * n <= 2.2e9:
+        assert rel_err(got["c"], a64 @ b64) <= TOL
+        assert rel_err(got["da"], d64 @ b64.T) <= TOL
+        assert rel_err(got["db"], a64.T @ d64) <= TOL
+        return
+    c, da, db = (got[x].astype(np.float64) for x in ("c", "da", "db"))
+    checks = [(c.sum(0), a64.sum(0) @ b64), (c.sum(1), a64 @ b64.sum(1)),
+              (da.sum(0), d64.sum(0) @ b64.T), (da.sum(1), d64 @ b64.sum(0)),
+              (db.sum(0), a64.sum(1) @ d64), (db.sum(1), a64.T @ d64.sum(1))]
+    for got_v, want_v in checks:
+        assert np.abs(got_v - want_v).max() / np.abs(want_v).max() <= TOL
+    rng = np.random.default_rng(5)
+    for _ in range(64):
+        i, j, l = int(rng.integers(m)), int(rng.integers(n)), int(rng.integers(k))
+        assert abs(c[i, j] - a64[i] @ b64[:, j]) <= TOL * np.abs(c).max()
+        assert abs(da[i, l] - d64[i] @ b64[l]) <= TOL * np.abs(da).max()
+        assert abs(db[l, j] - a64[:, l] @ d64[:, j]) <= TOL * np.abs(db).max()
+
+
 def _check_cnn(got, want, tol):
     assert abs(got["loss"] - want["loss"]) < 1e-4
     for k in want["grads"]:
