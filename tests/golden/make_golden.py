@@ -3,7 +3,7 @@
 
 Run in a container that has the reference sources:
 
-    make -C oracle            # builds oracle/_ref/libtinytorch_ref.so from /root/reference
+    make -C oracle            # builds oracle/_ref/libtinytorch_ref.so from the reference checkout (REF=...)
     python tests/golden/make_golden.py
 
 Every array written here is an output of the reference's own C code
