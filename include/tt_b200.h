@@ -70,6 +70,11 @@ int         ttb_trace_read(int kind, double *total_ms, long *launches, double *w
  * 0 = choose by shape, 1 = always the tcgen05 3xTF32 kernel (fails when the
  * shape cannot be fed by TMA), 2 = always the exact-fp32 kernel. */
 void    ttb_set_gemm_path(int path);
+/* How the tensor-core GEMM would run a product of this shape on `sms` SMs in a job of `world` ranks, as
+ * ten integers {tile width, pair kernel?, K block, CTAs or pairs used, tiles, uniform K slices, K blocks
+ * per slice, tail tiles, tail K slices, K blocks per tail slice}.  Needs no GPU; for tests and tuning.
+ * No reference counterpart. */
+int     ttb_gemm_plan(int M, int N, int K, int sms, int world, int out[10]);
 /* Stand-alone forms of the two backward GEMMs the reference keeps private:
  *   ttb_matmul_nt: R[M,N] = X[M,K] * Y[N,K]^T   (src/autograd.c:66-84)
  *   ttb_matmul_tn: R[M,N] = X[K,M]^T * Y[K,N]   (src/autograd.c:87-103) */

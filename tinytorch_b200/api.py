@@ -116,6 +116,7 @@ EXT_ABI = {
     "ttb_dist_allreduce": (CI, [VP]),
     "ttb_dist_join": (CI, []),
     "ttb_dist_finalize": (None, []),
+    "ttb_gemm_plan": (CI, [CI, CI, CI, CI, CI, ctypes.POINTER(ctypes.c_int)]),
     "ttb_dist_peer_export": (CI, [ctypes.c_size_t, CI, ctypes.c_char_p]),
     "ttb_dist_peer_import": (CI, [CI, CI, ctypes.c_char_p]),
     "ttb_dist_peer_active": (CI, []),

@@ -947,20 +947,11 @@ static int g_tc_fit_world = 4;       /* from this many ranks on (on two GPUs the
 static int g_tc_mn3d = 1;            /* TT_TC_MN3D=0: tuning aid, one TMA per 32 columns for MN-major tiles */
 static int g_tc_split_k = 1024;      /* reductions longer than this use the split accumulators */
 
-static int tc_setup(void) {
-    if (g_encode && g_status_host) return 0;
-    if (tt_ctx_init() != 0) return -1;
-    void *fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (!tt_cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint") ||
-        qres != cudaDriverEntryPointSuccess || !fn) {
-        tt_set_error("cuTensorMapEncodeTiled is not available from this driver");
-        return -1;
-    }
-    g_encode = (EncodeTiledFn)fn;
-    if (!tt_cuda_ok(cudaHostAlloc((void **)&g_status_host, sizeof(uint32_t), cudaHostAllocMapped), "cudaHostAlloc")) return -1;
-    *g_status_host = 0;
-    if (!tt_cuda_ok(cudaHostGetDevicePointer((void **)&g_status_dev, g_status_host, 0), "cudaHostGetDevicePointer")) return -1;
+/* Tuning knobs from the environment (no GPU needed). */
+static void tc_read_env(void) {
+    static bool done = false;
+    if (done) return;
+    done = true;
     const char *e = getenv("TT_TC_PASSES");
     if (e && atoi(e) == 1) g_tc_passes = 1;
     e = getenv("TT_TC_PREFETCH");
@@ -985,6 +976,23 @@ static int tc_setup(void) {
     if (e && *e) g_tc_force_bn = atoi(e);
     e = getenv("TT_TC_SPLIT_K");
     if (e && *e) g_tc_split_k = atoi(e);
+}
+
+static int tc_setup(void) {
+    if (g_encode && g_status_host) return 0;
+    if (tt_ctx_init() != 0) return -1;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (!tt_cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint") ||
+        qres != cudaDriverEntryPointSuccess || !fn) {
+        tt_set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return -1;
+    }
+    g_encode = (EncodeTiledFn)fn;
+    if (!tt_cuda_ok(cudaHostAlloc((void **)&g_status_host, sizeof(uint32_t), cudaHostAllocMapped), "cudaHostAlloc")) return -1;
+    *g_status_host = 0;
+    if (!tt_cuda_ok(cudaHostGetDevicePointer((void **)&g_status_dev, g_status_host, 0), "cudaHostGetDevicePointer")) return -1;
+    tc_read_env();
     return 0;
 }
 
@@ -1152,49 +1160,45 @@ static int launch_tc_major(const GemmArgs *g, const CUtensorMap &ma, const CUten
     return launch_tc<1, 1, BN, BK, STAGES, SPLIT_ACC>(g, ma, mb, a_3d, b_3d);
 }
 
-int gemm_tc(const GemmArgs *g) {
-    if (!gemm_tc_usable(g)) { tt_set_error("tcgen05 GEMM: operands are not 16-byte aligned with 16-byte row pitch"); return -1; }
-    if (tc_setup() != 0) return -1;
+/* What the host decides for one product, from its shape alone: tile width, one-CTA or pair kernel,
+ * how many CTAs (or pairs) take tiles, and how the reduction is cut.  Pure: no GPU, no allocation. */
+struct TcShapePlan {
+    int bn, pair, bk, units;
+    long tiles;
+    int splits, kb_per_split;                /* uniform split-K: every tile in `splits` slices */
+    int tail_tiles, tail_splits, tail_kb;    /* tail split: only the last wave's tiles */
+    int split_acc;
+};
+static void tc_plan_shape(int M, int N, int K, int gemm_sms, int world, TcShapePlan *o) {
+    tc_read_env();
     /* 128x256 tiles unless that leaves most SMs idle */
-    const long tiles256 = (long)((g->M + TC_BM - 1) / TC_BM) * ((g->N + 255) / 256);
-    int bn = (tiles256 * 10 < (long)g_tt.gemm_sms * 7 || g->N <= 128) ? 128 : 256;
+    const long tiles256 = (long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256);
+    int bn = (tiles256 * 10 < (long)gemm_sms * 7 || N <= 128) ? 128 : 256;
     if (g_tc_force_bn == 128 || g_tc_force_bn == 256) bn = g_tc_force_bn;
     /* CTA pairs (256x256 tile over two SMs) for the big shapes */
-    const bool pair = g_tc_2cta && bn == 256 && g->M >= 256 && (g_tt.gemm_sms >= 2);
-    CUtensorMap ma, mb;
-    /* K blocks of 32 (two stages for 128x256 tiles, three for 128x128).  TT_TC_BK=16 selects 64-byte
-     * rows with twice the stages; measured equal (the kernel is bound by shared-memory bandwidth,
-     * not by pipeline depth), so it stays a tuning aid. */
+    const bool pair = g_tc_2cta && bn == 256 && M >= 256 && gemm_sms >= 2;
+    /* K blocks of 32.  TT_TC_BK=16 selects 64-byte rows with twice the stages in the one-CTA kernel;
+     * measured equal there and slower in the pair kernel, so it stays a tuning aid. */
     int bk = 32;
     if (!pair && (g_tc_force_bk == 16 || g_tc_force_bk == 32)) bk = g_tc_force_bk;
-    const int b_box = pair ? 128 : bn;                 /* in a pair each CTA stages half of B's columns */
-    int a_3d = 0, b_3d = 0;
-    if (g->ta) {
-        if (g_tc_mn3d && g->M % 32 == 0 && encode_map_mn3d(&ma, g->A, g->M, g->K, g->lda, TC_BM / 32, bk) == 0) a_3d = 1;
-        else if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, bk, 1)) return -1;
-    } else if (encode_map(&ma, g->A, g->K, g->M, g->lda, bk, TC_BM, 0)) return -1;
-    if (g->tb) {
-        if (encode_map(&mb, g->B, g->K, g->N, g->ldb, bk, b_box, 0)) return -1;
-    } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, b_box / 32, bk) == 0) b_3d = 1;
-    else if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, bk, 1)) return -1;
-    /* Split-K when the tiles alone leave most SMs idle and the reduction is long enough to cut:
-     * slices of at least four K blocks, as many as fill the machine, partials in pool scratch. */
-    const int num_kb = (g->K + bk - 1) / bk;
-    const long tiles = (long)((g->M + (pair ? 255 : TC_BM - 1)) / (pair ? 256 : TC_BM)) * ((g->N + bn - 1) / bn);
-    int units = pair ? g_tt.gemm_sms / 2 : g_tt.gemm_sms;            /* CTAs, or CTA pairs, that take tiles */
+    const int num_kb = (K + bk - 1) / bk;
+    const long tiles = (long)((M + (pair ? 255 : TC_BM - 1)) / (pair ? 256 : TC_BM)) * ((N + bn - 1) / bn);
+    int units = pair ? gemm_sms / 2 : gemm_sms;                      /* CTAs, or CTA pairs, that take tiles */
     /* While gradients are being reduced on the other stream, a GEMM takes no more SMs than its wave
      * count needs: 64 pair tiles run as one wave on 64 pairs as fast as on 74, and the ten SM pairs
      * left over are where the collective's CTAs run instead of displacing GEMM CTAs (a GEMM CTA fills
      * an SM's shared memory, so the two never share an SM).  8 GPUs, large MLP: GEMM time per step
      * 2.07 -> 1.71 ms.  Shapes with few tiles keep every SM: they are cut along K instead. */
-    if (g_tc_fit && tt_dist_active() && ttb_dist_world() >= g_tc_fit_world && tiles * 2 > units) {
+    if (g_tc_fit && world >= g_tc_fit_world && world > 1 && tiles * 2 > units) {
         const long waves = (tiles + units - 1) / units;
         const long fit = (tiles + waves - 1) / waves;
         if (fit < units) units = (int)fit;
     }
-    g_plan.units = units;
-    g_plan.splits = 1; g_plan.kb_per_split = num_kb; g_plan.partial = nullptr;
-    g_plan.tail_tiles = 0; g_plan.tail_splits = 0; g_plan.tail_kb = 0; g_plan.tail_partial = nullptr;
+    o->bn = bn; o->pair = pair; o->bk = bk; o->units = units; o->tiles = tiles;
+    o->splits = 1; o->kb_per_split = num_kb;
+    o->tail_tiles = 0; o->tail_splits = 0; o->tail_kb = 0;
+    /* Split-K when the tiles alone leave most SMs idle and the reduction is long enough to cut:
+     * slices of at least four K blocks, as many as fill the machine, partials in pool scratch. */
     long want = 1;
     long tail_s = 0;                                   /* > 1: cut only the tiles of the last wave */
     if (g_tc_splitk && tiles * 2 <= units && num_kb >= 2 * (128 / bk)) {
@@ -1208,13 +1212,14 @@ int gemm_tc(const GemmArgs *g) {
          * products to write and re-read are a fraction).  Each candidate is priced as waves
          * of MMA time plus the traffic of its partial products; the cheapest wins. */
         const double sms = (double)units;
-        const double tile_us = 6.0 * (pair ? 256.0 : 128.0) * bn * (double)g->K / (4096.0 * 1.8e3 * 0.75);   /* one tile on one SM (pair), 75 % of the pipe */
+        /* one tile on one SM (a pair tile keeps two SMs busy for as long), 75 % of the pipe */
+        const double tile_us = 6.0 * 128.0 * bn * (double)K / (4096.0 * 1.8e3 * 0.75);
         double best = 1e30;
         for (long sp = 1; sp <= 4; sp++) {
             if ((long)(num_kb / sp) * bk < 512) break;
             const double items = (double)tiles * sp;
             const double waves = (double)((long)((items + sms - 1) / sms));
-            const double extra_us = sp > 1 ? (2.0 * sp + 1.0) * g->M * (double)g->N * 4.0 / 5.0e6 + 6.0 : 0.0;
+            const double extra_us = sp > 1 ? (2.0 * sp + 1.0) * M * (double)N * 4.0 / 5.0e6 + 6.0 : 0.0;
             const double t = tile_us * waves / sp + extra_us;
             if (t < best * 0.98) { best = t; want = sp; }
         }
@@ -1230,25 +1235,60 @@ int gemm_tc(const GemmArgs *g) {
         }
     }
     if (want >= 2) {
-        const long max_by_mem = (512l << 20) / ((long)g->M * g->N * 4 + 1);
+        const long max_by_mem = (512l << 20) / ((long)M * N * 4 + 1);
         if (want > max_by_mem) want = max_by_mem;
     }
     if (want >= 2) {
         const int per = (int)((num_kb + want - 1) / want);
-        const int splits = (num_kb + per - 1) / per;
-        float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * g->M * g->N);
-        if (!scratch) return -1;
-        g_plan.splits = splits; g_plan.kb_per_split = per; g_plan.partial = scratch;
+        o->splits = (num_kb + per - 1) / per; o->kb_per_split = per;
     } else if (tail_s >= 2) {
-        const long rest = tiles % units;
         const int per = (int)((num_kb + tail_s - 1) / tail_s);
-        const int splits = (num_kb + per - 1) / per;
-        float *scratch = (float *)tt_dev_alloc(sizeof(float) * (size_t)splits * rest * (pair ? 256 : TC_BM) * bn);
-        if (!scratch) return -1;
-        g_plan.tail_tiles = (int)rest; g_plan.tail_splits = splits; g_plan.tail_kb = per; g_plan.tail_partial = scratch;
+        o->tail_tiles = (int)(tiles % units); o->tail_splits = (num_kb + per - 1) / per; o->tail_kb = per;
     }
     /* long reductions keep the cross terms in their own accumulator (see the kernel) */
-    const bool split_acc = (long)g_plan.kb_per_split * bk > g_tc_split_k;
+    o->split_acc = (long)o->kb_per_split * bk > g_tc_split_k;
+}
+
+/* The plan for a shape as ten integers {bn, pair, bk, units, tiles, splits, kb_per_split, tail_tiles,
+ * tail_splits, tail_kb}: lets tests check the planner on a machine without a GPU. */
+extern "C" int ttb_gemm_plan(int M, int N, int K, int sms, int world, int out[10]) {
+    if (!out || M <= 0 || N <= 0 || K <= 0 || sms < 1 || world < 1) return -1;
+    TcShapePlan pl;
+    tc_plan_shape(M, N, K, sms, world, &pl);
+    out[0] = pl.bn; out[1] = pl.pair; out[2] = pl.bk; out[3] = pl.units; out[4] = (int)pl.tiles;
+    out[5] = pl.splits; out[6] = pl.kb_per_split; out[7] = pl.tail_tiles; out[8] = pl.tail_splits; out[9] = pl.tail_kb;
+    return 0;
+}
+
+int gemm_tc(const GemmArgs *g) {
+    if (!gemm_tc_usable(g)) { tt_set_error("tcgen05 GEMM: operands are not 16-byte aligned with 16-byte row pitch"); return -1; }
+    if (tc_setup() != 0) return -1;
+    TcShapePlan pl;
+    tc_plan_shape(g->M, g->N, g->K, g_tt.gemm_sms, tt_dist_active() ? ttb_dist_world() : 1, &pl);
+    const int bn = pl.bn, bk = pl.bk;
+    const bool pair = pl.pair != 0;
+    CUtensorMap ma, mb;
+    const int b_box = pair ? 128 : bn;                 /* in a pair each CTA stages half of B's columns */
+    int a_3d = 0, b_3d = 0;
+    if (g->ta) {
+        if (g_tc_mn3d && g->M % 32 == 0 && encode_map_mn3d(&ma, g->A, g->M, g->K, g->lda, TC_BM / 32, bk) == 0) a_3d = 1;
+        else if (encode_map(&ma, g->A, g->M, g->K, g->lda, 32, bk, 1)) return -1;
+    } else if (encode_map(&ma, g->A, g->K, g->M, g->lda, bk, TC_BM, 0)) return -1;
+    if (g->tb) {
+        if (encode_map(&mb, g->B, g->K, g->N, g->ldb, bk, b_box, 0)) return -1;
+    } else if (g_tc_mn3d && g->N % 32 == 0 && encode_map_mn3d(&mb, g->B, g->N, g->K, g->ldb, b_box / 32, bk) == 0) b_3d = 1;
+    else if (encode_map(&mb, g->B, g->N, g->K, g->ldb, 32, bk, 1)) return -1;
+    g_plan.units = pl.units;
+    g_plan.splits = pl.splits; g_plan.kb_per_split = pl.kb_per_split; g_plan.partial = nullptr;
+    g_plan.tail_tiles = pl.tail_tiles; g_plan.tail_splits = pl.tail_splits; g_plan.tail_kb = pl.tail_kb; g_plan.tail_partial = nullptr;
+    if (pl.splits > 1) {
+        g_plan.partial = (float *)tt_dev_alloc(sizeof(float) * (size_t)pl.splits * g->M * g->N);
+        if (!g_plan.partial) return -1;
+    } else if (pl.tail_tiles > 0) {
+        g_plan.tail_partial = (float *)tt_dev_alloc(sizeof(float) * (size_t)pl.tail_splits * pl.tail_tiles * (pair ? 256 : TC_BM) * bn);
+        if (!g_plan.tail_partial) return -1;
+    }
+    const bool split_acc = pl.split_acc != 0;
     int rc;
     if (pair) rc = launch_tc2(g, ma, mb, a_3d, b_3d, split_acc);
     else if (bn == 256 && bk == 16) rc = split_acc ? launch_tc_major<256, 16, 4, 1>(g, ma, mb, a_3d, b_3d) : launch_tc_major<256, 16, 4, 0>(g, ma, mb, a_3d, b_3d);
