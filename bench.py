@@ -533,6 +533,24 @@ def run_cnn(args):
                     "h2d_bytes_per_step": int(x.nbytes + sum(v.nbytes for v in p.values()) + 256 * 10 * 4),
                     "d2h_bytes_per_step": int(sum(v.nbytes for v in p.values()) + 2 * 256 * 10 * 4)},
             "gpu_launches": int(ns.LIB.ttb_launch_count() - l0)}
+    # the same step with parameters resident and the loss seed and SGD on the device
+    tr = W.CNNTrainer(ns, p, lr=0.01)
+    xt, yt = ns.Tensor.from_np(x), ns.Tensor.from_np(y.astype(np.float32))
+    for _ in range(3):
+        tr.step(xt, yt).release()
+    ns.sync()
+    e0, e1 = ns.LIB.ttb_event_create(), ns.LIB.ttb_event_create()
+    l1 = ns.LIB.ttb_launch_count()
+    reps = max(args.steps, 1)
+    ns.LIB.ttb_event_record(e0)
+    for _ in range(reps):
+        tr.step(xt, yt).release()
+    ns.LIB.ttb_event_record(e1)
+    ms = ns.LIB.ttb_event_elapsed_ms(e0, e1) / reps
+    line["device_resident"] = {"value": 256 / (ms * 1e-3), "unit": "samples/s", "ms_per_step": ms,
+                               "launches_per_step": int(ns.LIB.ttb_launch_count() - l1) // reps,
+                               "what": "parameters stay on the device, fused softmax-cross-entropy seed, SGD kernels; CUDA events"}
+    tr.close(); xt.release(); yt.release()
     if not args.no_cpu_baseline:
         from oracle import oracle as O
         ref = O.load_ref()

@@ -219,3 +219,23 @@ def test_device_resident_trainer_equals_gate_script_style(tt):
         tr.close()
     assert losses[-1] < losses[0]
     xt.release(); yt.release()
+
+
+def test_device_resident_cnn_equals_host_fed_step(tt):
+    """CNNTrainer (parameters on the device, fused seed) against the gate-script style step on the
+    same inputs: same kernels in the same order, so losses and gradients agree to rounding."""
+    x, y, p = W.config_cnn(32)
+    want = W.cnn_step_reference_style(tt, x, y, p)
+    tr = W.CNNTrainer(tt, p, lr=0.01)
+    xt, yt = tt.Tensor.from_np(x), tt.Tensor.from_np(y.astype(np.float32))
+    got = tr.grads_after(xt, yt)
+    assert abs(got["loss"] - want["loss"]) < 1e-5
+    for k in want["grads"]:
+        assert rel_err(got[k], want["grads"][k]) <= 1e-5, k
+    before = tr.weights()
+    tr.step(xt, yt).release()
+    after = tr.weights()
+    for k in before:                                   # one SGD step: w - lr * g
+        assert np.allclose(after[k], before[k] - np.float32(0.01) * got[k], rtol=1e-6, atol=1e-8), k
+    tr.close(); xt.release(); yt.release()
+

@@ -261,3 +261,94 @@ class MLPTrainer:
         for w in self.params:
             w.release()
         self.params = []
+
+
+class CNNTrainer:
+    """The benchmark CNN with everything on the device: persistent parameter leaves, the
+    convolutions, pools and dense layers of cnn_step_reference_style, fused
+    softmax-cross-entropy seed and SGD kernels.  Same arithmetic as the host-fed step; what
+    it leaves out is the per-step upload of every parameter and download of every gradient
+    that the reference's CIFAR gate does (tests/gate_cifar_cnn.py:160-185)."""
+
+    ORDER = ("w1", "b1", "w2", "b2", "fc1", "fc2")
+
+    def __init__(self, ns, params, lr=0.01, global_batch=None):
+        if not ns.has_ext:
+            raise RuntimeError("CNNTrainer needs the ttb_* entry points")
+        self.ns = ns
+        self.lr = float(lr)
+        self.global_batch = global_batch
+        self.pn = {}
+        for k in self.ORDER:
+            n = ns.Node.leaf(params[k], True)
+            n.mark_param(True)
+            self.pn[k] = n
+
+    def step(self, x_t, y_t):
+        """x_t: Tensor [b, 3, 32, 32]; y_t: Tensor [b] of class indices as fp32.
+        Returns the 1-element loss Tensor (still on the device)."""
+        ns = self.ns
+        batch = x_t.shape[0]
+        gb = self.global_batch or batch
+        nodes = []
+
+        def keep(n):
+            nodes.append(n)
+            return n
+
+        xn = keep(ns.Node.from_tensor(x_t, False))
+        h = cnn_forward(ns, keep, xn, self.pn)
+        h = keep(h.reshape((batch, int(np.prod(h.value_tensor().shape[1:])))))
+        h = keep(keep(h.padones()).matmul(self.pn["fc1"]))
+        h = keep(h.relu())
+        logits = keep(keep(h.padones()).matmul(self.pn["fc2"]))
+        loss, dlogits = ns.softmax_xent(logits.value_tensor(), y_t, 1.0 / gb)
+        logits.backward(dlogits)
+        ns.status(ns.LIB.ttb_dist_join(), "ttb_dist_join")
+        for w in self.pn.values():
+            ns.sgd_step(w.value_tensor(), w.grad_tensor(), self.lr)
+            w.zero_grad()
+        dlogits.release()
+        for n in nodes:
+            n.release()
+        return loss
+
+    def grads_after(self, x_t, y_t):
+        """Gradients of one step without the update (for tests): dict of arrays."""
+        lr, self.lr = self.lr, 0.0
+        ns = self.ns
+        batch = x_t.shape[0]
+        gb = self.global_batch or batch
+        nodes = []
+
+        def keep(n):
+            nodes.append(n)
+            return n
+
+        xn = keep(ns.Node.from_tensor(x_t, False))
+        h = cnn_forward(ns, keep, xn, self.pn)
+        h = keep(h.reshape((batch, int(np.prod(h.value_tensor().shape[1:])))))
+        h = keep(keep(h.padones()).matmul(self.pn["fc1"]))
+        h = keep(h.relu())
+        logits = keep(keep(h.padones()).matmul(self.pn["fc2"]))
+        loss, dlogits = ns.softmax_xent(logits.value_tensor(), y_t, 1.0 / gb)
+        logits.backward(dlogits)
+        ns.status(ns.LIB.ttb_dist_join(), "ttb_dist_join")
+        out = {k: w.grad() for k, w in self.pn.items()}
+        out["loss"] = float(loss.to_np()[0])
+        for w in self.pn.values():
+            w.zero_grad()
+        dlogits.release(); loss.release()
+        for n in nodes:
+            n.release()
+        self.lr = lr
+        return out
+
+    def weights(self):
+        return {k: w.value() for k, w in self.pn.items()}
+
+    def close(self):
+        for w in self.pn.values():
+            w.release()
+        self.pn = {}
+
