@@ -204,6 +204,82 @@ def test_im2col_col2im_bit_exact(tt, orc, geom):
         t.release()
 
 
+@pytest.mark.parametrize("shape", [(256, 3, 32, 32), (256, 32, 16, 16)], ids=["conv1", "conv2"])
+def test_full_size_im2col_col2im_are_adjoint(tt, shape):
+    """The benchmark CNN's two convolutions at batch 256, through properties that need no oracle
+    run: im2col only copies (every entry of col is an entry of x or 0, and the centre tap is x
+    itself), and col2im is its adjoint: <im2col(x), c> = <x, col2im(c)>."""
+    n, c, h, w = shape
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal(shape).astype(np.float32)
+    xt = T(tt, x)
+    col_t = tt.im2col(xt, 3, 3, 1, 1, 1, 1)
+    col = col_t.to_np()
+    assert col.shape == (c * 9, n * h * w)
+    centre = col.reshape(c, 9, n, h * w)[:, 4]                              # tap (kh, kw) = (1, 1)
+    assert np.array_equal(centre, x.reshape(n, c, h * w).transpose(1, 0, 2))
+    corner = col.reshape(c, 9, n, h, w)[:, 0]                               # tap (0, 0): x shifted by one, zero border
+    assert np.all(corner[:, :, 0, :] == 0) and np.all(corner[:, :, :, 0] == 0)
+    assert np.array_equal(corner[:, :, 1:, 1:], x.transpose(1, 0, 2, 3)[:, :, :-1, :-1])
+    d = rng.standard_normal(col.shape).astype(np.float32)
+    dt = T(tt, d)
+    back = tt.col2im(dt, n, c, h, w, 3, 3, 1, 1, 1, 1).to_np()
+    lhs = float(np.dot(col.reshape(-1).astype(np.float64), d.reshape(-1).astype(np.float64)))
+    rhs = float(np.dot(x.reshape(-1).astype(np.float64), back.reshape(-1).astype(np.float64)))
+    assert abs(lhs - rhs) <= 1e-6 * np.sqrt(col.size)
+    # an interior element is the sum of its nine taps, in (kh, kw) order
+    d5 = d.reshape(c, 3, 3, n, h, w)
+    for (nn, cc, hh, ww) in [(0, 0, 5, 7), (n - 1, c - 1, h - 2, w - 2), (n // 2, c // 2, 1, 1)]:
+        acc = np.float32(0)
+        for kh in range(3):
+            for kw in range(3):
+                acc = np.float32(acc + d5[cc, kh, kw, nn, hh + 1 - kh, ww + 1 - kw])
+        assert back[nn, cc, hh, ww] == acc
+    for t in (xt, col_t, dt):
+        t.release()
+
+
+def test_full_size_maxpool_forward_backward_properties(tt):
+    """[256, 32, 32, 32] with 2x2 windows: the forward equals a reshape-max in NumPy exactly; the
+    backward puts each window's gradient on the window's (unique) maximum and zero elsewhere."""
+    rng = np.random.default_rng(37)
+    x = rng.standard_normal((256, 32, 32, 32)).astype(np.float32)
+    g = rng.standard_normal((256, 32, 16, 16)).astype(np.float32)
+    out = run1(tt, "tt_maxpool2d", x, 2, 2, 2, 2)
+    want = x.reshape(256, 32, 16, 2, 16, 2).max(axis=(3, 5))
+    assert np.array_equal(out, want)
+    xt, gt = T(tt, x), T(tt, g)
+    dx = tt.maxpool_bwd(xt, gt, 2, 2, 2, 2).to_np()
+    up = lambda a: np.repeat(np.repeat(a, 2, axis=2), 2, axis=3)
+    winners = x == up(want)
+    assert winners.reshape(256, 32, 16, 2, 16, 2).sum(axis=(3, 5)).max() == 1        # no ties in this draw
+    assert np.array_equal(dx, np.where(winners, up(g), np.float32(0)))
+    for t in (xt, gt):
+        t.release()
+
+
+def test_full_size_softmax_xent_properties(tt):
+    """[8192, 1000] logits of the large MLP: every row of the gradient sums to zero (probabilities
+    sum to one, minus the one-hot), the label's entry is the only negative one, the loss equals the
+    float64 log-sum-exp form."""
+    rng = np.random.default_rng(41)
+    z = (rng.standard_normal((8192, 1000)) * 3).astype(np.float32)
+    y = rng.integers(0, 1000, size=8192)
+    zt, yt = T(tt, z), T(tt, y.astype(np.float32))
+    scale = 1.0 / 8192
+    loss, dz_t = tt.softmax_xent(zt, yt, scale)
+    dz = dz_t.to_np().astype(np.float64)
+    assert np.abs(dz.sum(1)).max() <= 5e-6 * scale
+    neg = dz < 0
+    assert np.array_equal(neg.sum(1), np.ones(8192, dtype=np.int64)) and np.all(neg[np.arange(8192), y])
+    z64 = z.astype(np.float64)
+    mx = z64.max(1)
+    want_loss = float((mx + np.log(np.exp(z64 - mx[:, None]).sum(1)) - z64[np.arange(8192), y]).mean())
+    assert abs(float(loss.to_np()[0]) - want_loss) <= 2e-6 * want_loss
+    for t in (zt, yt, loss, dz_t):
+        t.release()
+
+
 POOLS = [(2, 2, 6, 6, 2, 2, 2, 2), (2, 3, 7, 9, 3, 2, 1, 2), (1, 2, 5, 5, 3, 3, 1, 1), (2, 2, 8, 8, 2, 2, 3, 3),
          (8, 32, 32, 32, 2, 2, 2, 2), (1, 1, 4, 4, 4, 4, 1, 1), (3, 5, 10, 12, 2, 2, 2, 2)]
 
