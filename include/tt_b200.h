@@ -49,6 +49,11 @@ void        ttb_pinned_free(void *p);
  * normalise/gather/upload of the gate scripts (tests/gate_mnist_mlp.py:107-111).
  * `src` must stay untouched until the tensor has been used.  Returns 0 or -1. */
 int         ttb_upload_async(Tensor *dst, const float *src);
+/* The other direction: copy src's payload to dst (pinned host memory) on the copy stream, after the compute
+ * work enqueued so far; ttb_download_wait() blocks until all such copies have landed.  Lets a loop enqueue
+ * step i+1 before it reads step i's loss.  No reference counterpart (tt_data is the blocking read). */
+int         ttb_download_async(const Tensor *src, float *dst);
+int         ttb_download_wait(void);
 
 /* CUDA-event timing on the library's own stream. */
 void       *ttb_event_create(void);

@@ -5,6 +5,7 @@ GEMM (which reproduces the reference's accumulation order); a stated tolerance
 where the GPU orders a floating-point reduction differently or uses its own
 expf.  The golden fixtures (outputs of the reference library itself) are
 checked alongside the live oracle."""
+import ctypes
 import numpy as np
 import pytest
 
@@ -503,4 +504,25 @@ def test_optimizer_steps_match_numpy(tt):
         p -= lr_t * m / (np.sqrt(vv) + eps)
     assert np.allclose(wt.to_np(), p, rtol=1e-6, atol=1e-7)
     for t in (wt, gt, vt, mt, vt2):
+        t.release()
+
+
+def test_async_download_is_ordered_after_compute(tt):
+    """ttb_download_async copies on the copy stream what the compute stream has produced so far;
+    after ttb_download_wait the pinned array holds it (here: the result of a chain of kernels)."""
+    x = np.random.default_rng(2).standard_normal((512, 1024)).astype(np.float32)
+    xt = T(tt, x)
+    h = xt
+    keep = []
+    for _ in range(6):
+        h = tt.Tensor(tt.checked(tt.LIB.tt_addscalar(h.ptr, ctypes.c_float(1.0)), "tt_addscalar")); keep.append(h)
+    out = tt.pinned_array(x.shape)
+    out[...] = 0
+    tt.download_async(h, out)
+    tt.download_wait()
+    want = x.copy()
+    for _ in range(6):
+        want = want + np.float32(1.0)
+    assert np.array_equal(out, want)
+    for t in keep + [xt]:
         t.release()

@@ -116,6 +116,8 @@ EXT_ABI = {
     "ttb_dist_allreduce": (CI, [VP]),
     "ttb_dist_join": (CI, []),
     "ttb_dist_finalize": (None, []),
+    "ttb_download_async": (CI, [VP, ctypes.c_void_p]),
+    "ttb_download_wait": (CI, []),
     "ttb_gemm_plan": (CI, [CI, CI, CI, CI, CI, ctypes.POINTER(ctypes.c_int)]),
     "ttb_dist_peer_export": (CI, [ctypes.c_size_t, CI, ctypes.c_char_p]),
     "ttb_dist_peer_import": (CI, [CI, CI, ctypes.c_char_p]),
@@ -359,7 +361,16 @@ def bind(path=None):
                 raise ValueError("tinytorch: ttb_upload_async size mismatch")
             status(lib.ttb_upload_async(tensor.ptr, arr.ctypes.data_as(F32P)), "ttb_upload_async")
 
+        def download_async(tensor, arr):
+            """Queue a device -> host copy of `tensor` into `arr` (pinned, same element count);
+            the values are there after download_wait()."""
+            if arr.dtype != np.float32 or not arr.flags["C_CONTIGUOUS"] or arr.size != tensor.numel():
+                raise ValueError("tinytorch: ttb_download_async needs a contiguous float32 array of the tensor's size")
+            status(lib.ttb_download_async(tensor.ptr, arr.ctypes.data), "ttb_download_async")
+
         ns.upload_async = upload_async
+        ns.download_async = download_async
+        ns.download_wait = lambda: status(lib.ttb_download_wait(), "ttb_download_wait")
         ns._pinned = []
         ns.pinned_array = pinned_array
         ns.matmul_nt = lambda x, y: op("ttb_matmul_nt", x.ptr, y.ptr)

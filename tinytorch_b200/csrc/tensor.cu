@@ -198,6 +198,30 @@ extern "C" int ttb_upload_async(Tensor *dst, const float *src) {
     return 0;
 }
 
+/* Output side of the pipeline: copy a tensor's payload into caller memory (pinned, for a copy that is
+ * really asynchronous) on the copy stream, ordered after the compute work enqueued so far -- so the host
+ * can enqueue the next step before it looks at this one's result.  ttb_download_wait blocks until every
+ * such copy has landed (and reports a tensor-core kernel that gave up meanwhile). */
+extern "C" int ttb_download_async(const Tensor *src, float *dst) {
+    TTensor *t = TT(src);
+    if (!t || !dst) { tt_set_error("ttb_download_async: NULL argument"); return -1; }
+    const float *p = tt_dev_ro(src);
+    if (!p) return -1;
+    static cudaEvent_t fence = nullptr;
+    if (!fence && !tt_cuda_ok(cudaEventCreateWithFlags(&fence, cudaEventDisableTiming), "cudaEventCreate")) return -1;
+    if (!tt_cuda_ok(cudaEventRecord(fence, g_tt.stream), "cudaEventRecord") ||
+        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.copy_stream, fence, 0), "cudaStreamWaitEvent") ||
+        !tt_cuda_ok(cudaMemcpyAsync(dst, p, sizeof(float) * (size_t)t->pub.numel, cudaMemcpyDeviceToHost,
+                                    g_tt.copy_stream), "cudaMemcpyAsync(D2H)"))
+        return -1;
+    return 0;
+}
+extern "C" int ttb_download_wait(void) {
+    if (tt_ctx_init() != 0) return -1;
+    if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.copy_stream), "cudaStreamSynchronize(copy)")) return -1;
+    return gemm_tc_poll_status() ? -1 : 0;
+}
+
 extern "C" float *tt_data(const Tensor *ct) {
     TTensor *t = TT(ct);
     if (!t) return nullptr;
