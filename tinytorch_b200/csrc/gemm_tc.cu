@@ -19,7 +19,7 @@
  * means for this kernel.
  *
  * Structure of one CTA (persistent, one per SM, 448 threads):
- *   warp 0      TMA producer: cp.async.bulk.tensor loads (no multicast) of
+ *   warp 0      TMA producer: cp.async.bulk.tensor loads, each CTA fetching its own tiles, of
  *               the raw A and B tiles of a K block into a ring of stages, and
  *               L2 prefetches a few K blocks ahead so that those loads hit L2.
  *   warps 2-9   split: read the raw tiles from shared memory, write the lo
