@@ -9,6 +9,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <unordered_map>
+#include <vector>
+
 TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, 0, 0};    /* -1: take the setting from the environment */
 
 static char g_err[512] = "";
@@ -115,16 +118,61 @@ extern "C" int ttb_sync(void) {
 
 extern "C" long ttb_launch_count(void) { return g_tt.launches; }
 
+/* Device memory for tensors and scratch.  Underneath is the stream-ordered pool (cudaMallocAsync on
+ * the compute stream); in front of it sit free lists by exact size for blocks of up to 64 MB, because
+ * a training loop asks for the same few sizes thousands of times per second and the two driver
+ * calls per tensor were a third of the host's time per launch.  A block goes back on its list at
+ * release and is handed out again to the next request of that size: every use is ordered on the
+ * compute stream, so reuse needs no further synchronisation -- the same guarantee cudaFreeAsync on
+ * that stream gives.  The lists hold at most TT_CACHE_MB (default 4096) megabytes; beyond that, and
+ * for larger blocks, release goes to the pool.  TT_CACHE_MB=0 switches the lists off. */
+struct DevBlockCache {
+    std::unordered_map<size_t, std::vector<void *>> free_by_size;
+    std::unordered_map<void *, size_t> size_of;          /* blocks handed out that may come back to a list */
+    size_t cached_bytes = 0;
+    size_t limit_bytes = 0;
+    bool configured = false;
+};
+static DevBlockCache g_cache;
+static const size_t CACHE_MAX_BLOCK = (size_t)64 << 20;
+
 void *tt_dev_alloc(size_t bytes) {
     if (tt_ctx_init() != 0) return nullptr;
-    void *p = nullptr;
+    if (!g_cache.configured) {
+        g_cache.limit_bytes = (size_t)env_int("TT_CACHE_MB", 4096) << 20;
+        g_cache.configured = true;
+    }
     if (bytes == 0) bytes = 4;
+    bytes = (bytes + 255) & ~(size_t)255;
+    const bool cacheable = g_cache.limit_bytes > 0 && bytes <= CACHE_MAX_BLOCK;
+    if (cacheable) {
+        auto it = g_cache.free_by_size.find(bytes);
+        if (it != g_cache.free_by_size.end() && !it->second.empty()) {
+            void *p = it->second.back();
+            it->second.pop_back();
+            g_cache.cached_bytes -= bytes;
+            g_cache.size_of[p] = bytes;
+            return p;
+        }
+    }
+    void *p = nullptr;
     if (!tt_cuda_ok(cudaMallocAsync(&p, bytes, g_tt.stream), "cudaMallocAsync")) return nullptr;
+    if (cacheable) g_cache.size_of[p] = bytes;
     return p;
 }
 
 void tt_dev_free(void *p) {
     if (!p || g_tt.ready != 1) return;
+    auto it = g_cache.size_of.find(p);
+    if (it != g_cache.size_of.end()) {
+        const size_t bytes = it->second;
+        g_cache.size_of.erase(it);
+        if (g_cache.cached_bytes + bytes <= g_cache.limit_bytes) {
+            g_cache.free_by_size[bytes].push_back(p);
+            g_cache.cached_bytes += bytes;
+            return;
+        }
+    }
     cudaFreeAsync(p, g_tt.stream);
 }
 
