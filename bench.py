@@ -15,6 +15,7 @@ batch; `value` is global samples per second with the inputs resident in HBM.
 loss read back, every step.  One JSON line is printed by rank 0.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -150,6 +151,15 @@ def run_reference(args):
     rank, world, _ = D.env_rank_world()
     if rank != 0:
         return
+    if world > 1:
+        # torch.distributed.run sets OMP_NUM_THREADS=1 for its workers; the reference arm is one
+        # process on rank 0 and is to use every host core, as it does at N=1
+        n = os.cpu_count() or 1
+        os.environ["OMP_NUM_THREADS"] = str(n)
+        try:
+            ctypes.CDLL("libgomp.so.1").omp_set_num_threads(n)
+        except OSError:
+            pass
     step, kind = reference_step_fn()
     batch = args.ref_batch
     for _ in range(max(args.warmup, 1) if args.warmup else 0):
