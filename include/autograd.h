@@ -1,64 +1,105 @@
-/* tinytorch reverse-mode autograd C ABI, served by the B200 library.
+/* Reverse-mode autograd over device-resident tensors: the C ABI of the B200 library.
  *
- * Drop-in for the reference header include/autograd.h: the same 20 entry
- * points, opaque node type, ownership and error rules.  The graph itself
- * (nodes, refcounts, topological order, dispatch) is host code exactly as in
- * the reference (src/autograd.c:107-125, 630-745); every numeric loop behind
- * a builder or a backward rule is a CUDA kernel on the library's stream.
+ * A program written against the reference's include/autograd.h compiles against this
+ * header unchanged: the same twenty entry points, an opaque node type, the same
+ * ownership and error rules.  What differs is behind the calls.  The graph itself --
+ * nodes, reference counts, ordering, dispatch -- is host code, as in the reference
+ * (src/autograd.c:107-125, 630-745); every numeric loop of a builder or of a backward
+ * rule is a CUDA kernel enqueued on the library's stream, and nothing waits for the
+ * GPU until the caller asks for host data with tt_data().
  */
-#ifndef TINYTORCH_AUTOGRAD_H
-#define TINYTORCH_AUTOGRAD_H
+#ifndef TT_B200_AUTOGRAD_ABI_H
+#define TT_B200_AUTOGRAD_ABI_H
+
+#include <stddef.h>
 
 #include "tensor.h"
-#include <stddef.h>
 
 #ifdef __cplusplus
 extern "C" {
 #endif
 
-typedef struct AGNode AGNode;     /* opaque, refcounted */
+/* A vertex of the recorded graph.  Opaque and reference counted; it owns one reference
+ * to its value tensor and to each of its inputs. */
+struct AGNode;
+typedef struct AGNode AGNode;
 
-/* ---- builders: run the forward operator and record the edge ----
- * reference: include/autograd.h:14-31, src/autograd.c:127-275.
- * Each returns a node with refcount 1 that retains its parents, or NULL when
- * an argument is NULL or the forward operator rejects the shapes. */
-AGNode *ag_leaf(Tensor *t, int requires_grad);     /* retains t */
-AGNode *ag_add(AGNode *a, AGNode *b);
-AGNode *ag_mul(AGNode *a, AGNode *b);
-AGNode *ag_addscalar(AGNode *a, float s);
-AGNode *ag_mulscalar(AGNode *a, float s);
-AGNode *ag_matmul(AGNode *a, AGNode *b);           /* 2-D x 2-D */
-AGNode *ag_relu(AGNode *a);
-AGNode *ag_softmax(AGNode *a);                     /* last axis */
-AGNode *ag_padones(AGNode *a);                     /* [M,K] -> [M,K+1], last column = 1 */
-AGNode *ag_reshape(AGNode *a, const long *new_shape, int new_ndim);
-AGNode *ag_conv2d(AGNode *a, AGNode *w, AGNode *b, /* b may be NULL */
-                  int stride_h, int stride_w, int pad_h, int pad_w);
-AGNode *ag_maxpool2d(AGNode *a, int pool_h, int pool_w,
-                     int stride_h, int stride_w);
-AGNode *ag_avgpool2d(AGNode *a, int pool_h, int pool_w,
-                     int stride_h, int stride_w);
+/* ------------------------------------------------------------------------------------
+ * Life cycle (reference: include/autograd.h:14,47-48; src/autograd.c:127-133, 731-745)
+ * ---------------------------------------------------------------------------------- */
 
-/* ---- accessors (reference: include/autograd.h:34-36); borrowed pointers ---- */
-Tensor *ag_value(const AGNode *n);
-Tensor *ag_grad(const AGNode *n);                  /* NULL until a backward pass reached n */
-int     ag_requires_grad(const AGNode *n);
+/* Wrap an existing tensor as an input of the graph.  The node takes its own reference
+ * to `value`; the caller keeps (and later releases) the one it holds.  NULL in, NULL out. */
+AGNode *ag_leaf(Tensor *value, int requires_grad);
 
-/* ---- reverse pass (reference: include/autograd.h:38-45, src/autograd.c:682-727) ----
- * ag_backward seeds d(out) with ones.  ag_backward_from copies `seed`
- * (seed_numel host floats) into d(out); seed_numel must equal the element
- * count of out, otherwise the call returns without touching anything, and the
- * caller has to surface that as an error.  d(out) is overwritten by the seed,
- * every other node accumulates, and gradients stay on their nodes, so a
- * second pass over the same graph adds to the first. */
-void    ag_backward(AGNode *out);
-void    ag_backward_from(AGNode *out, const float *seed, size_t seed_numel);
+/* One more / one fewer reference.  Dropping the last one releases the node's tensors
+ * and then its inputs, iteratively, so that a chain of any depth unwinds without
+ * recursion on the C stack. */
+AGNode *ag_retain(AGNode *node);
+void    ag_release(AGNode *node);
 
-/* ---- node lifetime (reference: include/autograd.h:47-48, src/autograd.c:731-745) ---- */
-void    ag_release(AGNode *n);
-AGNode *ag_retain(AGNode *n);
+/* ------------------------------------------------------------------------------------
+ * What a node holds (reference: include/autograd.h:34-36; src/autograd.c:277-281).
+ * The pointers are borrowed: valid while the node lives, not to be released.
+ * ---------------------------------------------------------------------------------- */
+Tensor *ag_value(const AGNode *node);
+Tensor *ag_grad(const AGNode *node);              /* NULL until a reverse pass has reached the node */
+int     ag_requires_grad(const AGNode *node);
+
+/* ------------------------------------------------------------------------------------
+ * Builders (reference: include/autograd.h:15-31; src/autograd.c:135-275).
+ * Each runs the forward operator on the GPU, records the edge and returns a node with
+ * one reference, or NULL when an argument is NULL or the operator rejects the shapes
+ * (the rules are those of the tt_* operator of the same name in tensor.h).
+ * ---------------------------------------------------------------------------------- */
+
+/* element by element, equal shapes */
+AGNode *ag_add(AGNode *lhs, AGNode *rhs);
+AGNode *ag_mul(AGNode *lhs, AGNode *rhs);
+AGNode *ag_addscalar(AGNode *x, float c);
+AGNode *ag_mulscalar(AGNode *x, float c);
+AGNode *ag_relu(AGNode *x);
+
+/* [M,K] times [K,N]; on this library a tcgen05 3xTF32 product, or the exact fp32 kernel
+ * for small shapes */
+AGNode *ag_matmul(AGNode *lhs, AGNode *rhs);
+
+/* softmax along the last axis */
+AGNode *ag_softmax(AGNode *x);
+
+/* [M,K] -> [M,K+1] with a last column of ones: the reference's way of carrying a bias
+ * as one more row of the weight matrix.  Feeding a matmul, the column is never written
+ * here: the bias row is added in the product's epilogue. */
+AGNode *ag_padones(AGNode *x);
+
+/* same elements, new shape (dims[0..ndim-1], product unchanged) */
+AGNode *ag_reshape(AGNode *x, const long *dims, int ndim);
+
+/* NCHW convolution with filters [F,C,HH,WW] and an optional bias [F] (bias may be NULL) */
+AGNode *ag_conv2d(AGNode *x, AGNode *filters, AGNode *bias, int stride_h, int stride_w, int pad_h, int pad_w);
+
+/* pooling over windows window_h x window_w without padding */
+AGNode *ag_maxpool2d(AGNode *x, int window_h, int window_w, int stride_h, int stride_w);
+AGNode *ag_avgpool2d(AGNode *x, int window_h, int window_w, int stride_h, int stride_w);
+
+/* ------------------------------------------------------------------------------------
+ * Reverse pass (reference: include/autograd.h:38-45; src/autograd.c:682-727).
+ *
+ * ag_backward starts from d(root) = 1 everywhere.  ag_backward_from starts from `seed`,
+ * `count` floats in host memory; `count` has to equal the number of elements of the
+ * root's value -- when it does not, or when the root does not require a gradient, the
+ * call returns having changed nothing, and it is the caller's job to notice (the Python
+ * wrappers compare the sizes first and raise).
+ *
+ * d(root) is overwritten by the seed; every other node ADDS what arrives to the gradient
+ * it already holds, and gradients stay on their nodes afterwards.  A second pass over the
+ * same graph therefore adds to the first (the reference's tests pin the resulting values,
+ * tests/test_grad.py:293-313, and so do this repository's).
+ * ---------------------------------------------------------------------------------- */
+void ag_backward(AGNode *root);
+void ag_backward_from(AGNode *root, const float *seed, size_t count);
 
 #ifdef __cplusplus
 }
 #endif
-#endif
+#endif /* TT_B200_AUTOGRAD_ABI_H */

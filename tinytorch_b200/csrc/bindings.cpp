@@ -1,11 +1,14 @@
-/* pybind11 module `tinytorch_pybind`: the Node class of the reference's
- * Python-facing module (src/bindings.cpp:54-150) over the B200 library.
+/* pybind11 module `tinytorch_pybind` over the B200 library.
  *
- * Same class name, method names, keyword arguments and defaults; a NULL from
- * the C ABI becomes ValueError (src/bindings.cpp:22-30); arrays are copied in
- * with tt_fromdata and out through tt_data.  The module links against
- * libtinytorch.so instead of compiling the C sources into itself, so Python
- * and C callers share one device context. */
+ * Python surface of the reference's module (src/bindings.cpp:54-150): one class, Node,
+ * with the same method names, keyword arguments and defaults, so scripts written for it
+ * run unchanged.  A NULL from the C ABI becomes ValueError carrying the library's own
+ * error text; arrays go in through tt_fromdata and come out through tt_data.  Unlike the
+ * reference's module, which compiles the C sources into itself, this one links against
+ * libtinytorch.so, so Python and C callers of one process share one device context.
+ *
+ * The bindings are a table of lambdas over a handle type; the handle is a shared_ptr whose
+ * deleter is ag_release, so Python's garbage collector drives the node reference counts. */
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
@@ -13,6 +16,7 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "autograd.h"
@@ -20,117 +24,134 @@
 #include "tt_b200.h"
 
 namespace py = pybind11;
-using f32_array = py::array_t<float, py::array::c_style | py::array::forcecast>;
 
 namespace {
 
-[[noreturn]] void fail(const char *what) {
-    std::string msg = std::string("tinytorch: ") + what + " failed (invalid arguments or shape mismatch)";
-    const char *why = ttb_last_error();
-    if (why && *why) msg += std::string(": ") + why;
-    throw py::value_error(msg);
-}
+using HostArray = py::array_t<float, py::array::c_style | py::array::forcecast>;
 
-std::shared_ptr<AGNode> own(AGNode *n, const char *what) {
-    if (!n) fail(what);
-    return std::shared_ptr<AGNode>(n, [](AGNode *p) { ag_release(p); });
-}
-
-py::array_t<float> to_numpy(Tensor *t) {
-    if (!t) return py::array_t<float>();
-    std::vector<long> dims((size_t)tt_ndim(t));
-    tt_shape(t, dims.data());
-    std::vector<py::ssize_t> shape(dims.begin(), dims.end());
-    py::array_t<float> out(shape);
-    const float *src = tt_data(t);
-    if (!src) fail("tt_data");
-    std::memcpy(out.mutable_data(), src, sizeof(float) * (size_t)tt_numel(t));
-    return out;
-}
-
-class Node {
-public:
-    explicit Node(std::shared_ptr<AGNode> n) : n_(std::move(n)) {}
-
-    static Node leaf(f32_array arr, bool requires_grad) {
-        py::buffer_info info = arr.request();
-        std::vector<long> shape((size_t)info.ndim);
-        for (py::ssize_t i = 0; i < info.ndim; i++) shape[(size_t)i] = (long)info.shape[(size_t)i];
-        Tensor *t = tt_fromdata(static_cast<const float *>(info.ptr), shape.data(), (int)info.ndim);
-        if (!t) fail("tt_fromdata");
-        AGNode *n = ag_leaf(t, requires_grad ? 1 : 0);
-        tt_release(t);                      /* the node holds its own reference */
-        return Node(own(n, "ag_leaf"));
-    }
-
-    py::array_t<float> value() const { return to_numpy(ag_value(n_.get())); }
-
-    py::object grad() const {
-        Tensor *g = ag_grad(n_.get());
-        if (!g) return py::none();
-        return to_numpy(g);
-    }
-
-    void backward(py::object seed) {
-        if (seed.is_none()) { ag_backward(n_.get()); return; }
-        f32_array arr = seed.cast<f32_array>();
-        py::buffer_info info = arr.request();
-        Tensor *v = ag_value(n_.get());
-        if (!v || (size_t)info.size != (size_t)tt_numel(v))
-            throw py::value_error("tinytorch: seed length mismatch");
-        ag_backward_from(n_.get(), static_cast<const float *>(info.ptr), (size_t)info.size);
-    }
-
-    Node add(const Node &o) const { return Node(own(ag_add(n_.get(), o.n_.get()), "ag_add")); }
-    Node mul(const Node &o) const { return Node(own(ag_mul(n_.get(), o.n_.get()), "ag_mul")); }
-    Node addscalar(float s) const { return Node(own(ag_addscalar(n_.get(), s), "ag_addscalar")); }
-    Node mulscalar(float s) const { return Node(own(ag_mulscalar(n_.get(), s), "ag_mulscalar")); }
-    Node matmul(const Node &o) const { return Node(own(ag_matmul(n_.get(), o.n_.get()), "ag_matmul")); }
-    Node relu() const { return Node(own(ag_relu(n_.get()), "ag_relu")); }
-    Node softmax() const { return Node(own(ag_softmax(n_.get()), "ag_softmax")); }
-    Node padones() const { return Node(own(ag_padones(n_.get()), "ag_padones")); }
-    Node reshape(std::vector<long> shape) const {
-        return Node(own(ag_reshape(n_.get(), shape.data(), (int)shape.size()), "ag_reshape"));
-    }
-    Node conv2d(const Node &w, py::object b, int sh, int sw, int ph, int pw) const {
-        AGNode *bias = b.is_none() ? nullptr : b.cast<Node>().n_.get();
-        return Node(own(ag_conv2d(n_.get(), w.n_.get(), bias, sh, sw, ph, pw), "ag_conv2d"));
-    }
-    Node maxpool2d(int ph, int pw, int sh, int sw) const {
-        return Node(own(ag_maxpool2d(n_.get(), ph, pw, sh, sw), "ag_maxpool2d"));
-    }
-    Node avgpool2d(int ph, int pw, int sh, int sw) const {
-        return Node(own(ag_avgpool2d(n_.get(), ph, pw, sh, sw), "ag_avgpool2d"));
-    }
-
-private:
-    std::shared_ptr<AGNode> n_;
+/* Python-visible handle of one graph node. */
+struct Node {
+    std::shared_ptr<AGNode> ref;
+    AGNode *raw() const { return ref.get(); }
 };
+
+[[noreturn]] void raise_for(const char *call) {
+    std::string text = "tinytorch: ";
+    text += call;
+    text += " failed (invalid arguments or shape mismatch)";
+    if (const char *why = ttb_last_error(); why && *why) {
+        text += ": ";
+        text += why;
+    }
+    throw py::value_error(text);
+}
+
+/* Take ownership of a node the C ABI just returned (one reference), or raise. */
+Node adopt(AGNode *fresh, const char *call) {
+    if (fresh == nullptr) raise_for(call);
+    return Node{std::shared_ptr<AGNode>(fresh, &ag_release)};
+}
+
+/* Device tensor -> new NumPy array (waits for the GPU). */
+py::array_t<float> export_tensor(Tensor *t) {
+    if (t == nullptr) return py::array_t<float>();
+    const int rank = tt_ndim(t);
+    std::vector<long> extents(static_cast<size_t>(rank));
+    tt_shape(t, extents.data());
+    py::array_t<float> result(std::vector<py::ssize_t>(extents.begin(), extents.end()));
+    const float *host = tt_data(t);
+    if (host == nullptr) raise_for("tt_data");
+    std::memcpy(result.mutable_data(), host, sizeof(float) * static_cast<size_t>(tt_numel(t)));
+    return result;
+}
+
+/* NumPy array -> leaf node. */
+Node import_leaf(HostArray values, bool requires_grad) {
+    const py::buffer_info view = values.request();
+    std::vector<long> extents;
+    extents.reserve(static_cast<size_t>(view.ndim));
+    for (py::ssize_t extent : view.shape) extents.push_back(static_cast<long>(extent));
+    Tensor *payload = tt_fromdata(static_cast<const float *>(view.ptr), extents.data(), static_cast<int>(extents.size()));
+    if (payload == nullptr) raise_for("tt_fromdata");
+    AGNode *leaf = ag_leaf(payload, requires_grad ? 1 : 0);
+    tt_release(payload);                    /* the node holds its own reference */
+    return adopt(leaf, "ag_leaf");
+}
+
+/* Reverse pass from ones, or from a seed array of exactly the root's size. */
+void run_backward(const Node &root, const py::object &seed) {
+    if (seed.is_none()) {
+        ag_backward(root.raw());
+        return;
+    }
+    const HostArray values = seed.cast<HostArray>();
+    const py::buffer_info view = values.request();
+    const Tensor *value = ag_value(root.raw());
+    if (value == nullptr || static_cast<long>(view.size) != tt_numel(value))
+        throw py::value_error("tinytorch: seed length mismatch");
+    ag_backward_from(root.raw(), static_cast<const float *>(view.ptr), static_cast<size_t>(view.size));
+}
+
+/* Binders for the three call shapes most builders have. */
+template <AGNode *(*Build)(AGNode *)>
+auto unary(const char *call) {
+    return [call](const Node &x) { return adopt(Build(x.raw()), call); };
+}
+template <AGNode *(*Build)(AGNode *, AGNode *)>
+auto binary(const char *call) {
+    return [call](const Node &x, const Node &y) { return adopt(Build(x.raw(), y.raw()), call); };
+}
+template <AGNode *(*Build)(AGNode *, float)>
+auto with_scalar(const char *call) {
+    return [call](const Node &x, float c) { return adopt(Build(x.raw(), c), call); };
+}
+template <AGNode *(*Build)(AGNode *, int, int, int, int)>
+auto pooling(const char *call) {
+    return [call](const Node &x, int window_h, int window_w, int stride_h, int stride_w) {
+        return adopt(Build(x.raw(), window_h, window_w, stride_h, stride_w), call);
+    };
+}
 
 }  // namespace
 
 PYBIND11_MODULE(tinytorch_pybind, m) {
     m.doc() = "tinytorch autograd nodes on the B200 library";
-    py::class_<Node>(m, "Node")
-        .def_static("leaf", &Node::leaf, py::arg("arr"), py::arg("requires_grad") = true)
-        .def("value", &Node::value)
-        .def("grad", &Node::grad)
-        .def("backward", &Node::backward, py::arg("seed") = py::none())
-        .def("add", &Node::add)
-        .def("mul", &Node::mul)
-        .def("addscalar", &Node::addscalar)
-        .def("mulscalar", &Node::mulscalar)
-        .def("matmul", &Node::matmul)
-        .def("relu", &Node::relu)
-        .def("softmax", &Node::softmax)
-        .def("padones", &Node::padones)
-        .def("reshape", &Node::reshape)
-        .def("conv2d", &Node::conv2d, py::arg("w"), py::arg("b") = py::none(), py::arg("stride_h") = 1,
-             py::arg("stride_w") = 1, py::arg("pad_h") = 0, py::arg("pad_w") = 0)
-        .def("maxpool2d", &Node::maxpool2d, py::arg("pool_h") = 2, py::arg("pool_w") = 2,
-             py::arg("stride_h") = 2, py::arg("stride_w") = 2)
-        .def("avgpool2d", &Node::avgpool2d, py::arg("pool_h") = 2, py::arg("pool_w") = 2,
-             py::arg("stride_h") = 2, py::arg("stride_w") = 2)
-        .def("__add__", &Node::add)
-        .def("__mul__", &Node::mul);
+    using namespace pybind11::literals;
+
+    py::class_<Node> node(m, "Node");
+    node.def_static("leaf", &import_leaf, "arr"_a, "requires_grad"_a = true);
+
+    /* what the node holds */
+    node.def("value", [](const Node &x) { return export_tensor(ag_value(x.raw())); });
+    node.def("grad", [](const Node &x) -> py::object {
+        Tensor *g = ag_grad(x.raw());
+        if (g == nullptr) return py::none();
+        return export_tensor(g);
+    });
+    node.def("backward", &run_backward, "seed"_a = py::none());
+
+    /* builders */
+    node.def("add", binary<&ag_add>("ag_add"));
+    node.def("mul", binary<&ag_mul>("ag_mul"));
+    node.def("__add__", binary<&ag_add>("ag_add"));
+    node.def("__mul__", binary<&ag_mul>("ag_mul"));
+    node.def("matmul", binary<&ag_matmul>("ag_matmul"));
+    node.def("addscalar", with_scalar<&ag_addscalar>("ag_addscalar"));
+    node.def("mulscalar", with_scalar<&ag_mulscalar>("ag_mulscalar"));
+    node.def("relu", unary<&ag_relu>("ag_relu"));
+    node.def("softmax", unary<&ag_softmax>("ag_softmax"));
+    node.def("padones", unary<&ag_padones>("ag_padones"));
+    node.def("reshape", [](const Node &x, std::vector<long> extents) {
+        return adopt(ag_reshape(x.raw(), extents.data(), static_cast<int>(extents.size())), "ag_reshape");
+    });
+    node.def("conv2d",
+             [](const Node &x, const Node &filters, const py::object &bias, int stride_h, int stride_w, int pad_h, int pad_w) {
+                 AGNode *b = bias.is_none() ? nullptr : bias.cast<const Node &>().raw();
+                 return adopt(ag_conv2d(x.raw(), filters.raw(), b, stride_h, stride_w, pad_h, pad_w), "ag_conv2d");
+             },
+             "w"_a, "b"_a = py::none(), "stride_h"_a = 1, "stride_w"_a = 1, "pad_h"_a = 0, "pad_w"_a = 0);
+    node.def("maxpool2d", pooling<&ag_maxpool2d>("ag_maxpool2d"), "pool_h"_a = 2, "pool_w"_a = 2, "stride_h"_a = 2,
+             "stride_w"_a = 2);
+    node.def("avgpool2d", pooling<&ag_avgpool2d>("ag_avgpool2d"), "pool_h"_a = 2, "pool_w"_a = 2, "stride_h"_a = 2,
+             "stride_w"_a = 2);
 }
