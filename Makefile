@@ -12,7 +12,7 @@ BUILD   := build
 OBJDIR  := $(BUILD)/obj
 # -fmad=false: the exact-fp32 and elementwise kernels round every multiply and
 # add separately, like the reference's C; only explicit fmaf() fuses.
-EXACT   := context tensor ops autograd dist peer_reduce kernels_elementwise kernels_spatial gemm_simt
+EXACT   := context tensor ops autograd dist peer_reduce kernels_elementwise kernels_spatial kernels_pipeline gemm_simt
 FAST    := gemm_tc
 OBJS    := $(addprefix $(OBJDIR)/,$(addsuffix .o,$(EXACT) $(FAST)))
 HDRS    := $(wildcard include/*.h) $(SRC)/tt_internal.h

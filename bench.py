@@ -161,19 +161,38 @@ def run_reference(args):
         except OSError:
             pass
     step, kind = reference_step_fn()
-    batch = args.ref_batch
-    for _ in range(max(args.warmup, 1) if args.warmup else 0):
+    # Every step is the FULL global batch unless the first one predicts that warm-up + timed steps
+    # would not fit the budget; only then is a slice of the batch timed and the line says so.
+    step(64)                                             # page in, build the thread pool
+    batch, extrapolated = GLOBAL_BATCH, False
+    n_steps = max(args.warmup, 1) + max(args.steps, 1)
+    if args.ref_batch:
+        batch, extrapolated = args.ref_batch, args.ref_batch != GLOBAL_BATCH
+    else:
+        per_sample = step(256) / 256                     # probe: over-estimates the full step (fixed costs spread over fewer samples)
+        if per_sample * GLOBAL_BATCH * n_steps > args.ref_budget_s:
+            first = step(GLOBAL_BATCH) if kind == "reference" and per_sample * GLOBAL_BATCH < args.ref_budget_s / 4 else None
+            if first is not None and first * n_steps <= args.ref_budget_s:
+                pass
+            else:
+                if first is not None:
+                    per_sample = first / GLOBAL_BATCH
+                fit = args.ref_budget_s / (n_steps * per_sample)
+                batch = min(GLOBAL_BATCH, max(64, 1 << int(np.floor(np.log2(max(fit, 64))))))
+                extrapolated = batch != GLOBAL_BATCH
+    for _ in range(max(args.warmup, 1)):
         step(batch)
     times = [step(batch) for _ in range(max(args.steps, 1))]
     sec = statistics.median(times)
     value = batch / sec
     sample = (f"{batch} of {GLOBAL_BATCH} samples per step through the reference's autograd C ABI "
-              f"(weights re-uploaded as leaves, softmax to NumPy, seed from NumPy, SGD in NumPy), median of {len(times)}")
+              f"(weights re-uploaded as leaves, softmax to NumPy, seed from NumPy, SGD in NumPy), median of {len(times)}; "
+              f"the reference caps its forward sgemm at 12 threads")
     line = {
         "impl": "reference", "metric": "train_samples_per_sec", "value": value, "unit": "samples/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * GLOBAL_BATCH / batch,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "config": workload_config(args.gpus), "extrapolated": extrapolated,
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": host_threads(), "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -231,11 +250,35 @@ def gemm_block(ns, peaks, cases=((1024, 5), (4096, 5))):
         gbs = bytes_alg / (med * 1e-3) / 1e9
         t_tensor, t_hbm = 6.0 * m * k * n / (tf32_peak * 1e12), bytes_alg / (hbm * 1e9)
         out.append({"shape": [m, k, n], "ms": med, "operand_sets_per_pass": sets, "tflops": tflops,
-                    "frac_of_tf32_peak": tflops / tf32_peak, "tensor_pipe_frac_estimate": 3 * tflops / tf32_peak,
+                    "frac_of_tf32_peak": tflops / tf32_peak,
                     "algorithmic_gbs": gbs, "frac_of_hbm_peak": gbs / hbm,
                     "bound": "hbm" if t_hbm > t_tensor else "tensor"})
         for an, bn, dct in ops:
             an.release(); bn.release(); dct.release()
+    return out
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per tcgen05 GEMM launch, averaged over the launches of
+# one step of this workload at N GPUs (ncu, one step captured; see the named summary).  None: not captured.
+MLP_GEMM_TRAFFIC = {}
+MLP_GEMM_TRAFFIC_SOURCE = None
+# sm__pipe_tensor_cycles_active of the pair kernel, from the ncu capture named here (not an estimate)
+TENSOR_PIPE_NCU = {"value": 0.70, "case": "4096^3, gemm_tc2_kernel", "source": "profiles/gemm_tc2_kernel_square4096.md"}
+
+
+def weights_checksum(ws, samples_per_param=25):
+    """float64 sums of every parameter plus a few fixed entries: equal (to rounding of the different
+    reduction orders) for every number of GPUs after the same number of steps."""
+    rng = np.random.default_rng(12345)
+    out = {"sum": [], "abs_sum": [], "samples": [], "replicas_max_abs_diff": 0.0}
+    for w in ws:
+        w64 = w.astype(np.float64)
+        out["sum"].append(float(w64.sum()))
+        out["abs_sum"].append(float(np.abs(w64).sum()))
+        idx = rng.integers(0, w.size, size=samples_per_param)
+        out["samples"].extend(float(v) for v in w.reshape(-1)[idx])
+        out["replicas_max_abs_diff"] = max(out["replicas_max_abs_diff"], D.max_abs_diff_from_rank0(w))
+    out["replicas_identical"] = out["replicas_max_abs_diff"] == 0.0
     return out
 
 
@@ -272,24 +315,35 @@ def run_ours(args):
     for _ in range(args.warmup):
         resident_step().release()
     ns.sync(); D.barrier()
+    # what the host needs to enqueue a step, measured on two steps into an empty launch queue (in the
+    # timed loop below the queue fills and the host is paced by the GPU, which says nothing about it)
+    host_t0 = time.perf_counter()
+    for _ in range(2):
+        resident_step().release()
+    host_enqueue_ms = (time.perf_counter() - host_t0) * 1e3 / 2
+    ns.sync(); D.barrier()
     window0 = time.time()
     ns.LIB.ttb_trace_reset(); ns.LIB.ttb_trace_enable(1)
     launches0 = ns.LIB.ttb_launch_count()
     e0, e1 = ns.LIB.ttb_event_create(), ns.LIB.ttb_event_create()
     ns.LIB.ttb_event_record(e0)
     last = None
-    host_t0 = time.perf_counter()
     for _ in range(args.steps):
         if last is not None:
             last.release()
         last = resident_step()
-    host_enqueue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps   # the host only enqueues; it runs ahead of the GPU
     ns.LIB.ttb_event_record(e1)
     ms_total = ns.LIB.ttb_event_elapsed_ms(e0, e1)
     ns.sync(); D.barrier()
     launches = ns.LIB.ttb_launch_count() - launches0
+    comm = ns.comm_read() if world > 1 else None
     ns.LIB.ttb_trace_enable(0)
-    final_loss = float(last.to_np()[0]); last.release()
+    # the loss of the last timed step over the GLOBAL batch: every rank holds the mean over its own rows
+    final_loss = D.all_sum([float(last.to_np()[0]) * b])[0] / GLOBAL_BATCH
+    last.release()
+    # the parameters after warm-up + 2 + timed steps: float64 checksums (comparable across N: the same
+    # number of steps has run on the same global batch) and the largest difference between replicas
+    checksum = weights_checksum(trainer.weights())
     ms_total = D.all_max(float(ms_total))
     ms_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_step * 1e-3)
@@ -347,9 +401,11 @@ def run_ours(args):
     clock_info = clocks.stop((window0, time.time())) if rank == 0 else None
     e2e_value = GLOBAL_BATCH / (e2e_ms / args.steps * 1e-3)
 
-    if rank != 0:
+    if world > 1:
+        # every rank ends communication together (peer blocks are closed by all before any is freed)
         trainer.close()
-        ns.LIB.ttb_dist_finalize()
+        D.finalize(ns)
+    if rank != 0:
         return
 
     tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
@@ -362,16 +418,18 @@ def run_ours(args):
         "config": workload_config(world),
         "fwd_bwd_tflops": flops_step / (ms_step * 1e-3) / 1e12,
         "fwd_bwd_tflops_frac_of_tf32_peak": flops_step / (ms_step * 1e-3) / 1e12 / (tf32_peak * world),
-        "final_loss": final_loss, "host_enqueue_ms_per_step": host_enqueue_ms,
+        "final_loss": final_loss, "weights_checksum": checksum,
+        "host_enqueue_ms_per_step": host_enqueue_ms,
         "roofline": {
             "kernel": "gemm_tc2_kernel (tcgen05.mma.cta_group::2 kind::tf32 on CTA pairs, 3xTF32 split, TMA-staged)",
             "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-            "frac": achieved / tf32_peak if tf32_peak else None, "traffic": None,
+            "frac": achieved / tf32_peak if tf32_peak else None, "traffic": MLP_GEMM_TRAFFIC.get(world),
             "launches": tc_n, "avg_launch_ms": tc_ms / tc_n if tc_n else None,
             "peak_source": f"{peak_kind} bf16_tflops_sustained / 2 (no TF32 figure is recorded; TF32 dense is half of bf16)",
             "note": "achieved counts algorithmic FLOPs (2MNK per GEMM); the 3xTF32 split issues three MMAs per "
-                    "product, so tensor-pipe occupancy is about 3x this fraction",
-            "tensor_pipe_frac_estimate": 3 * achieved / tf32_peak if tf32_peak else None,
+                    "product, so a kernel whose tensor pipe never idles reads 0.333 here",
+            "traffic_source": MLP_GEMM_TRAFFIC_SOURCE if MLP_GEMM_TRAFFIC.get(world) else None,
+            "tensor_pipe_active_ncu": TENSOR_PIPE_NCU,
         },
         "kernel_classes": classes,
         "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(xs.nbytes + ys.nbytes) * world,
@@ -379,21 +437,35 @@ def run_ours(args):
         "gpu_launches": int(launches),
         "clocks": clock_info,
     }
+    if comm is not None and comm["collectives"]:
+        # rank 0's view of its collectives: CUDA-event pairs on the communication stream (the wait for
+        # the slowest rank is inside them), bus bandwidth 2(G-1)/G * bytes / time, and per step the time
+        # the communication stream ran on after the compute stream's last kernel (what was not hidden)
+        sec = comm["collective_ms"] * 1e-3
+        line["comm"] = {
+            "allreduces_per_step": comm["collectives"] / args.steps,
+            "bytes_per_step": comm["bytes"] / args.steps,
+            "collective_ms_per_step": comm["collective_ms"] / args.steps,
+            "longest_collective_ms": comm["longest_collective_ms"],
+            "bus_gbs": (2.0 * (world - 1) / world) * comm["bytes"] / sec / 1e9 if sec > 0 else None,
+            "exposed_ms": comm["exposed_ms"] / max(comm["joins"], 1),
+            "transport": "peer-memory kernel" if peer_floats else "ncclAllReduce",
+            "nccl_max_ctas": os.environ.get("NCCL_MAX_CTAS"),
+        }
     if world == 1:
         if not args.no_gemm:
             line["gemm_fwd_bwd"] = gemm_block(ns, peaks)
         if not args.no_cpu_baseline:
             step, kind = reference_step_fn()
-            batch = args.ref_batch
-            step(min(batch, 64))                         # page in, build thread pool
-            t = [step(batch) for _ in range(2)]
-            sec = min(t)
+            batch = args.ref_batch or (GLOBAL_BATCH if kind == "reference" else 256)   # the scalar port is far slower
+            step(64)                                     # page in, build thread pool
+            sec = step(batch)
             line["cpu_baseline"] = {
                 "value": batch / sec, "unit": "samples/s", "cores": host_threads(), "kind": kind,
-                "sample": f"{batch} of {GLOBAL_BATCH} samples of the same step on the host cores, best of 2 "
-                          f"({sec:.2f} s each); the reference caps its forward sgemm at 12 threads"}
-    trainer.close()
-    ns.LIB.ttb_dist_finalize()
+                "sample": f"one step on {batch} of {GLOBAL_BATCH} samples on the host cores ({sec:.2f} s); "
+                          f"the reference caps its forward sgemm at 12 threads"}
+        trainer.close()
+        ns.LIB.ttb_dist_finalize()
     print(json.dumps(line), flush=True)
 
 
@@ -597,8 +669,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--ref-batch", type=int, default=1024,
-                    help="samples per CPU step of the reference arm / CPU baseline (a slice of the global batch)")
+    ap.add_argument("--ref-batch", type=int, default=0,
+                    help="samples per CPU step of the reference arm / CPU baseline; 0 = the full global batch "
+                         "(the reference arm falls back to a slice, and says so, only if the run would not fit --ref-budget-s)")
+    ap.add_argument("--ref-budget-s", type=float, default=780.0,
+                    help="wall-clock the reference arm may spend on warm-up + timed steps")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="tuning aid: a smaller global batch reproduces the per-GPU shapes of a larger job on fewer GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")

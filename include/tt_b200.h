@@ -35,6 +35,9 @@ int         ttb_sync(void);
 long        ttb_launch_count(void);
 /* Device address of a tensor's payload (uploads a pending host write first). */
 float      *ttb_device_ptr(Tensor *t);
+/* {free bytes on the GPU, bytes the library's memory pool holds from the driver, bytes of the pool in
+ * use}: lets a caller (and the tests) see whether a call allocated anything.  Returns 0 or -1. */
+int         ttb_mem_info(unsigned long long out[3]);
 
 /* Page-locked host memory, so that tt_fromdata / ag_backward_from copy from it
  * with a true asynchronous DMA instead of staging through the driver. */
@@ -51,9 +54,25 @@ void        ttb_pinned_free(void *p);
 int         ttb_upload_async(Tensor *dst, const float *src);
 /* The other direction: copy src's payload to dst (pinned host memory) on the copy stream, after the compute
  * work enqueued so far; ttb_download_wait() blocks until all such copies have landed.  Lets a loop enqueue
- * step i+1 before it reads step i's loss.  No reference counterpart (tt_data is the blocking read). */
+ * step i+1 before it reads step i's loss.  src may be released right after the call (its memory is not
+ * reused before the copy has run); dst must stay valid until ttb_download_wait.  No reference counterpart
+ * (tt_data is the blocking read). */
 int         ttb_download_async(const Tensor *src, float *dst);
 int         ttb_download_wait(void);
+
+/* Normalise + gather, the first stage of the gate scripts' input pipeline
+ * (tests/gate_mnist_mlp.py:86-90,107-111; tests/gate_cifar_cnn.py:162-163):
+ *     xb = ((pixels[idx] / 255) - mean) / std
+ * The raw 8-bit dataset [n_rows, channels, plane] is uploaded once (ttb_bytes_upload returns its
+ * device address, ttb_bytes_free releases it) and stays resident; every step
+ * ttb_gather_normalize_u8 fills `dst` (b * channels * plane floats, any shape) with the b rows
+ * idx[0..b) picks, normalised per channel, bit-identical to NumPy's float32 arithmetic.  idx, mean
+ * and std are host arrays (mean/std: one value per channel, at most 16 channels); idx may be reused
+ * as soon as the call returns.  Returns 0, or -1 on bad arguments or an index outside [0, n_rows). */
+void       *ttb_bytes_upload(const void *host, size_t nbytes);
+void        ttb_bytes_free(void *dev);
+int         ttb_gather_normalize_u8(Tensor *dst, const void *src_dev, long n_rows, const int *idx, long b,
+                                    int channels, const float *mean, const float *std);
 
 /* CUDA-event timing on the library's own stream. */
 void       *ttb_event_create(void);
@@ -97,16 +116,19 @@ Tensor *ttb_softmax_bwd(const Tensor *s, const Tensor *g);
 Tensor *ttb_colsum(const Tensor *g);
 /* The same column sums for a caller that may not allocate device memory at the
  * moment of the call: an application whose own arena owns all of the GPU's
- * memory, a loop that cannot afford an allocator call, code running while a
- * stream is being recorded.  The partial sums go to a 2 MiB array built into the
- * library instead of pool memory, so the call itself performs no allocation.
- * g_dev is [rows, cols] with row pitch ldg (floats), out_dev holds cols floats;
- * both are device addresses (ttb_device_ptr) and the work is queued on the
- * library's stream.  accumulate != 0 adds into out_dev.  At most 16384 columns;
- * more is refused with -1 and a message.  The first call on a device looks the
- * array's address up; make it before recording that device's stream.  All calls
- * share the array: do not let two of them overlap on the GPU.  There is no
- * counterpart in the reference, which is host code over malloc. */
+ * memory, or a loop that cannot afford an allocator call.  The partial sums go
+ * to a 2 MiB array built into the library instead of pool memory, so the call
+ * itself performs no allocation.  g_dev is [rows, cols] with row pitch ldg
+ * (floats), out_dev holds cols floats; both are device addresses
+ * (ttb_device_ptr) on the library's GPU, and the work is queued on the
+ * library's own compute stream (the one every other entry point uses), not on a
+ * stream of the caller's.  accumulate != 0 adds into out_dev.  At most 16384
+ * columns; more is refused with -1 and a message, and so is a call made while a
+ * GPU other than the library's is current.  The first call looks the array's
+ * address up (cudaGetSymbolAddress); make that call before any stream capture
+ * is begun in the process.  All calls share the array: do not let two of them
+ * overlap on the GPU.  There is no counterpart in the reference, which is host
+ * code over malloc. */
 int     ttb_colsum_static(const float *g_dev, int rows, int cols, long ldg, float *out_dev, int accumulate);
 /* Batched im2col and its adjoint (src/ops_spatial.c:37-69,
  * src/autograd.c:406-434).  x is [N,C,H,W]; col is [C*kh*kw, N*Hout*Wout]. */
@@ -134,6 +156,21 @@ Tensor *ttb_avgpool_bwd(const Tensor *g, int N, int C, int H, int W, int pool_h,
  * the mean loss.  NULL on shape errors. */
 Tensor *ttb_softmax_xent(const Tensor *logits, const Tensor *labels, float scale,
                          Tensor **dlogits);
+
+/* ---- evaluation -----------------------------------------------------------
+ * pred = logits.argmax(axis=1); correct = (pred == y).sum()
+ * (tests/gate_mnist_mlp.py:74-80, tests/gate_cifar_cnn.py:114-122) without moving the logits to
+ * the host.  ttb_argmax returns the [rows] tensor of class indices (as fp32; first maximum, a NaN
+ * counts as the maximum, like NumPy); ttb_argmax_correct returns how many rows' argmax equals the
+ * label (labels: one class index per row as fp32), or -1.  It waits for the GPU (four bytes back). */
+Tensor *ttb_argmax(const Tensor *logits);
+long    ttb_argmax_correct(const Tensor *logits, const Tensor *labels);
+/* Forward-only mode for evaluation batches: while off, the ag_* builders compute values but record
+ * no graph (a node keeps no reference to its parents and requires no gradient), so an activation
+ * is freed as soon as the caller releases its node, and a matmul followed by relu never stores
+ * its pre-activation.  On by default; ttb_grad_enabled reads the setting. */
+void    ttb_set_grad_enabled(int on);
+int     ttb_grad_enabled(void);
 
 /* ---- autograd extras ------------------------------------------------------
  * ag_backward_from with the seed already on the device: same contract, no
@@ -177,6 +214,20 @@ void    ag_mark_param(AGNode *leaf, int on);
 void    ag_param_sgd(AGNode *leaf, float lr);
 int     ttb_dist_allreduce(Tensor *t);               /* sum over ranks, in place, async */
 int     ttb_dist_join(void);
+/* Lifetime rule for everything that runs beside the compute stream (ttb_dist_allreduce, the
+ * reductions and fused updates of marked parameters, ttb_download_async): the tensor may be
+ * released at any time after the call -- the library orders the reuse of its memory after the
+ * work in flight -- but its CONTENTS are final only after ttb_dist_join / ttb_download_wait. */
+/* Timing of the collectives while ttb_trace_enable is on, summed since ttb_trace_reset:
+ * out = {collectives, bytes reduced, ms inside collectives (event pairs on the communication
+ * stream), joins, exposed ms (communication stream's tail minus compute stream's tail at each
+ * ttb_dist_join, when positive), longest collective in ms}.  Returns 0 or -1. */
+int     ttb_dist_comm_read(double out[6]);
+/* Ends the job's communication: frees this rank's peer-memory block (if any) and destroys the
+ * NCCL communicator.  ORDER when the peer-memory path is in use: all ranks rendezvous, every
+ * rank calls ttb_dist_peer_close, all ranks rendezvous again, then every rank calls
+ * ttb_dist_finalize -- a block must not be freed while another process still has it open, and
+ * no rank may exit in between.  tinytorch_b200.dist.finalize() does exactly that. */
 void    ttb_dist_finalize(void);
 /* Optional: reduce gradients with this library's own peer-memory kernel (plain NVLink loads and stores
  * from CTAs that share SMs with the GEMM) instead of ncclAllReduce.  After ttb_dist_init every rank calls
@@ -187,6 +238,14 @@ void    ttb_dist_finalize(void);
 int     ttb_dist_peer_export(size_t max_floats, int world, char handle_out[64]);
 int     ttb_dist_peer_import(int rank, int world, const char *handles);
 int     ttb_dist_peer_active(void);
+/* First half of the tear-down: close the other ranks' blocks and switch the peer kernel off
+ * (see ttb_dist_finalize for the order). */
+void    ttb_dist_peer_close(void);
+/* Limit of the peer kernel's device-side waits on other ranks, in milliseconds (default about
+ * 2000).  When a wait runs out the kernel stops waiting, ttb_dist_join returns -1 with the phase
+ * and the rank it waited for, the failure is passed on to every peer (their next wait or launch
+ * reports it too) and this process refuses further peer reductions.  Returns 0 or -1. */
+int     ttb_dist_set_wait_limit_ms(int ms);
 
 #ifdef __cplusplus
 }

@@ -190,6 +190,60 @@ def test_config4_large_mlp_scaled(tt, orc, golden_steps):
         assert rel_err(a, b) <= TOL
 
 
+def _mlp_grads_float64(x, y, ws, masks, global_batch):
+    """Forward + backward of the MLP in float64 NumPy with the relu masks GIVEN (so that two
+    implementations whose pre-activations differ in the last bits can each be checked with their own
+    masks): returns loss, logits and the weight gradients."""
+    acts, h = [], x.astype(np.float64)
+    for i, w in enumerate(ws):
+        acts.append(h)
+        z = h @ w[:-1].astype(np.float64) + w[-1].astype(np.float64)
+        h = z * masks[i] if i + 1 < len(ws) else z
+    z = h - h.max(1, keepdims=True)
+    p = np.exp(z); p /= p.sum(1, keepdims=True)
+    loss = float(-np.log(np.maximum(p[np.arange(x.shape[0]), y], 1e-12)).mean())
+    d = p.copy(); d[np.arange(x.shape[0]), y] -= 1.0; d /= global_batch
+    grads = [None] * len(ws)
+    for i in range(len(ws) - 1, -1, -1):
+        g = np.empty(ws[i].shape, np.float64)
+        g[:-1] = acts[i].T @ d
+        g[-1] = d.sum(0)
+        grads[i] = g
+        if i > 0:
+            d = (d @ ws[i][:-1].astype(np.float64).T) * masks[i - 1]
+    return loss, h, grads
+
+
+def test_config4_full_batch_step_against_the_reference(tt, ref):
+    """ONE step of the benchmark's own workload at its full size (batch 8192, the shapes bench.py
+    times) against the reference library running the same step on the host cores.  Forward values
+    are compared directly.  Gradients pass through the relu kink (see test_config4_large_mlp_scaled):
+    each side is compared with a float64 restatement that differentiates with that side's own masks,
+    which also pins the restatement to the reference at this size."""
+    x, y, ws = W.config_mlp_large(batch=8192)
+    got = W.mlp_step_reference_style(tt, x, y, ws, lr=0.1, global_batch=8192, return_pre=True)
+    want = W.mlp_step_reference_style(ref, x, y, ws, lr=0.1, global_batch=8192, return_pre=True)
+    assert abs(got["loss"] - want["loss"]) < 1e-4
+    assert rel_err(got["logits"], want["logits"]) <= TOL
+    ours, theirs = [], []
+    for zg, zo in zip(got["pre"], want["pre"]):
+        assert rel_err(zg, zo) <= TOL
+        flipped = (zg > 0) != (zo > 0)
+        assert flipped.mean() < 1e-4
+        assert np.all(np.abs(zo[flipped]) <= TOL * np.abs(zo).max())
+        ours.append(zg > 0); theirs.append(zo > 0)
+    loss64, logits64, g_ours = _mlp_grads_float64(x, y, ws, ours, 8192)
+    assert abs(got["loss"] - loss64) < 1e-4
+    assert rel_err(got["logits"], logits64) <= TOL
+    for a, b in zip(got["grads"], g_ours):
+        assert rel_err(a, b) <= TOL
+    _, _, g_theirs = _mlp_grads_float64(x, y, ws, theirs, 8192)
+    for a, b in zip(want["grads"], g_theirs):
+        assert rel_err(a, b) <= TOL
+    for a, b, c in zip(got["weights"], ws, g_ours):               # the SGD step of the gate script
+        assert rel_err(a, b.astype(np.float64) - 0.1 * c) <= 1e-6
+
+
 def test_device_resident_trainer_equals_gate_script_style(tt):
     """Persistent parameters + fused loss + SGD kernel give the same weights as
     the literal per-step re-leafing of the reference's gate script."""

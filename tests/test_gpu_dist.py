@@ -62,7 +62,56 @@ for a in got:
     t = torch.from_numpy(a.copy()); t0 = t.clone()
     dist.broadcast(t0, src=0)
     assert torch.equal(t, t0)
-tr.close(); ns.LIB.ttb_dist_finalize(); D.barrier()
+tr.close(); D.finalize(ns)
+sys.stdout.write("rank%dok\n" % rank)
+"""
+
+# One rank skips a reduction, so the other's device-side wait on it runs out.  The failure is made on
+# the host (a call that is not issued); no kernel traps, faults or spins without a limit.
+FAILURE_WORKER = r"""
+import os, sys, time
+import numpy as np
+sys.path.insert(0, sys.argv[1])
+import tinytorch_b200
+from tinytorch_b200 import dist as D
+rank, world, local = D.init_process_group("gloo")
+ns = tinytorch_b200.default()
+ns.status(ns.LIB.ttb_init(local), "ttb_init")
+D.connect(ns, rank, world, peer_floats=1 << 20)
+assert ns.LIB.ttb_dist_peer_active()
+assert ns.LIB.ttb_dist_set_wait_limit_ms(300) == 0
+a = np.full(4096, float(rank + 1), np.float32)
+t = ns.Tensor.from_np(a)
+# a healthy round first
+ns.status(ns.LIB.ttb_dist_allreduce(t.ptr), "ttb_dist_allreduce")
+ns.status(ns.LIB.ttb_dist_join(), "ttb_dist_join")
+assert np.all(t.to_np() == 3.0)
+D.barrier()
+if rank == 0:
+    # rank 1 never launches this one: the wait on its flag gives up after the shortened limit
+    assert ns.LIB.ttb_dist_allreduce(t.ptr) == 0
+    t0 = time.time()
+    ns.LIB.ttb_sync()
+    took = time.time() - t0
+    assert ns.LIB.ttb_dist_join() == -1
+    msg = ns.LIB.ttb_last_error().decode()
+    assert "wait expired" in msg and "rank 1" in msg, msg
+    assert took < 5.0, took
+    # the failure is sticky: this process launches no further peer reductions
+    assert ns.LIB.ttb_dist_allreduce(t.ptr) == -1
+D.barrier()
+if rank == 1:
+    # out of step with rank 0 now; the poison word rank 0 left makes this launch report instead of
+    # passing its waits on stale flags
+    assert ns.LIB.ttb_dist_allreduce(t.ptr) == 0
+    ns.LIB.ttb_sync()
+    assert ns.LIB.ttb_dist_join() == -1
+    assert "gave up" in ns.LIB.ttb_last_error().decode() or "given up" in ns.LIB.ttb_last_error().decode()
+# the device still answers on both ranks
+u = ns.Tensor.from_np(a)
+assert np.all(u.to_np() == float(rank + 1))
+t.release(); u.release()
+D.finalize(ns)
 sys.stdout.write("rank%dok\n" % rank)
 """
 
@@ -78,6 +127,23 @@ def test_two_gpu_data_parallel_matches_full_batch(tt, tmp_path, peer_floats):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", "29633", str(script), ROOT, str(peer_floats)]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "rank0ok" in out.stdout and "rank1ok" in out.stdout
+
+
+def test_a_peer_that_skips_a_reduction_is_reported_not_waited_for(tt, tmp_path):
+    """Bounded device-side waits: with the limit shortened to 0.3 s, a reduction whose partner never
+    launches ends with a status the host reads (phase and rank), the other rank learns of it through
+    the poison word, both processes keep a working GPU context and tear down in order.  Plain peer
+    loads and stores only (NVLS off)."""
+    if tt.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "failure_worker.py"
+    script.write_text(FAILURE_WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29637", str(script), ROOT]
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert "rank0ok" in out.stdout and "rank1ok" in out.stdout

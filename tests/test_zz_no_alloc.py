@@ -48,6 +48,30 @@ def test_static_column_sums_match_the_allocating_entry_point_twice(tt):
             t.release()
 
 
+def _mem(tt):
+    import ctypes
+    buf = (ctypes.c_ulonglong * 3)()
+    assert tt.LIB.ttb_mem_info(buf) == 0
+    return tuple(buf)
+
+
+def test_static_column_sums_allocate_nothing(tt):
+    """Free memory on the GPU, what the library's pool holds and what it has handed out are the same
+    before and after the calls.  The very first call in a process is the set-up call (it looks the
+    array's address up, and with CUDA's lazy module loading the driver loads the kernels' code then),
+    so it is made before the first reading."""
+    g_t = tt.Tensor.from_np(np.ones((4096, 2048), np.float32))
+    out_t = tt.Tensor.zeros((2048,))
+    assert _static_colsum(tt, g_t, out_t) == 0, tt.LIB.ttb_last_error()
+    tt.sync()
+    before = _mem(tt)
+    for _ in range(3):
+        assert _static_colsum(tt, g_t, out_t) == 0, tt.LIB.ttb_last_error()
+    tt.sync()
+    assert _mem(tt) == before
+    g_t.release(); out_t.release()
+
+
 def test_static_column_sums_refuse_what_does_not_fit(tt):
     g_t = tt.Tensor.zeros((2, 16385))
     out_t = tt.Tensor.zeros((16385,))

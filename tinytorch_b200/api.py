@@ -78,6 +78,7 @@ EXT_ABI = {
     "ttb_sync": (CI, []),
     "ttb_launch_count": (ctypes.c_long, []),
     "ttb_device_ptr": (VP, [VP]),
+    "ttb_mem_info": (CI, [ctypes.POINTER(ctypes.c_ulonglong)]),
     "ttb_pinned_alloc": (VP, [ctypes.c_size_t]),
     "ttb_pinned_free": (None, [VP]),
     "ttb_upload_async": (CI, [VP, F32P]),
@@ -122,6 +123,16 @@ EXT_ABI = {
     "ttb_dist_peer_export": (CI, [ctypes.c_size_t, CI, ctypes.c_char_p]),
     "ttb_dist_peer_import": (CI, [CI, CI, ctypes.c_char_p]),
     "ttb_dist_peer_active": (CI, []),
+    "ttb_dist_peer_close": (None, []),
+    "ttb_dist_set_wait_limit_ms": (CI, [CI]),
+    "ttb_dist_comm_read": (CI, [ctypes.POINTER(ctypes.c_double)]),
+    "ttb_bytes_upload": (VP, [VP, ctypes.c_size_t]),
+    "ttb_bytes_free": (None, [VP]),
+    "ttb_gather_normalize_u8": (CI, [VP, VP, ctypes.c_long, ctypes.POINTER(ctypes.c_int), ctypes.c_long, CI, F32P, F32P]),
+    "ttb_argmax": (VP, [VP]),
+    "ttb_argmax_correct": (ctypes.c_long, [VP, VP]),
+    "ttb_set_grad_enabled": (None, [CI]),
+    "ttb_grad_enabled": (CI, []),
 }
 
 # kernel classes of ttb_trace_read
@@ -368,6 +379,62 @@ def bind(path=None):
                 raise ValueError("tinytorch: ttb_download_async needs a contiguous float32 array of the tensor's size")
             status(lib.ttb_download_async(tensor.ptr, arr.ctypes.data), "ttb_download_async")
 
+        class ByteDataset:
+            """A raw 8-bit dataset [rows, channels, ...] resident on the device, and the
+            normalise + gather stage that cuts fp32 batches from it."""
+
+            def __init__(self, arr_u8, mean, std):
+                arr = np.ascontiguousarray(arr_u8, dtype=np.uint8)
+                self.shape = arr.shape
+                self.rows = int(arr.shape[0])
+                self.channels = int(arr.shape[1]) if arr.ndim > 2 else 1
+                self.mean = np.ascontiguousarray(np.broadcast_to(np.asarray(mean, np.float32).ravel(), (self.channels,)))
+                self.std = np.ascontiguousarray(np.broadcast_to(np.asarray(std, np.float32).ravel(), (self.channels,)))
+                self.dev = lib.ttb_bytes_upload(arr.ctypes.data, arr.nbytes)
+                if not self.dev:
+                    raise MemoryError(f"tinytorch: ttb_bytes_upload failed{why()}")
+
+            def batch_into(self, tensor, idx):
+                """tensor <- ((rows[idx] / 255) - mean) / std; idx: integer array of the batch's rows."""
+                idx = np.ascontiguousarray(idx, dtype=np.int32)
+                status(lib.ttb_gather_normalize_u8(tensor.ptr, self.dev, self.rows,
+                                                   idx.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), int(idx.size),
+                                                   self.channels, self.mean.ctypes.data_as(F32P),
+                                                   self.std.ctypes.data_as(F32P)), "ttb_gather_normalize_u8")
+
+            def free(self):
+                if self.dev:
+                    lib.ttb_bytes_free(self.dev)
+                    self.dev = None
+
+        class no_grad:
+            """Context manager: forward-only mode (no graph, no saved activations)."""
+
+            def __enter__(self):
+                self.prev = lib.ttb_grad_enabled()
+                lib.ttb_set_grad_enabled(0)
+
+            def __exit__(self, *exc):
+                lib.ttb_set_grad_enabled(self.prev)
+                return False
+
+        def argmax_correct(logits, labels):
+            n = int(lib.ttb_argmax_correct(logits.ptr, labels.ptr))
+            if n < 0:
+                raise RuntimeError(f"tinytorch: ttb_argmax_correct failed{why()}")
+            return n
+
+        def comm_read():
+            buf = (ctypes.c_double * 6)()
+            status(lib.ttb_dist_comm_read(buf), "ttb_dist_comm_read")
+            return {"collectives": int(buf[0]), "bytes": buf[1], "collective_ms": buf[2], "joins": int(buf[3]),
+                    "exposed_ms": buf[4], "longest_collective_ms": buf[5]}
+
+        ns.ByteDataset = ByteDataset
+        ns.no_grad = no_grad
+        ns.argmax = lambda t: op("ttb_argmax", t.ptr)
+        ns.argmax_correct = argmax_correct
+        ns.comm_read = comm_read
         ns.upload_async = upload_async
         ns.download_async = download_async
         ns.download_wait = lambda: status(lib.ttb_download_wait(), "ttb_download_wait")

@@ -15,7 +15,18 @@
  * in the weight gradient), its [M,K+1] value is produced only if somebody
  * asks for it, and the matmul's input gradient goes straight to the padones
  * node's parent.  Leaf gradients are unchanged; ag_grad() of such a padones
- * node stays NULL.  TT_FUSE_PADONES=0 restores the literal behaviour. */
+ * node stays NULL.  TT_FUSE_PADONES=0 restores the literal behaviour.
+ *
+ * A second one, for the relu that follows a matmul (TT_FUSE_RELU=0 restores the literal
+ * behaviour): ag_matmul does not launch its product at once but leaves its value deferred.
+ * If the next builder to touch the node is ag_relu, ONE GEMM runs whose epilogue writes
+ * max(x*w + b, 0) as the relu node's value, and the pre-activation is never stored; anybody
+ * who does read it later (ag_value + tt_data, another builder, the root of a backward pass)
+ * gets it from a plain GEMM launched at that moment -- from the operands as they are then.
+ * Backward, the relu's mask is taken from its OUTPUT (y > 0 exactly when x > 0, NaN and the
+ * infinities included), and when a matmul's input gradient is the only contribution to a relu
+ * node it is masked in that GEMM's epilogue and written straight into the gradient of the
+ * relu's parent; ag_grad() of such a relu node stays NULL, every other gradient is unchanged. */
 #include "tt_internal.h"
 
 #include <stdlib.h>
@@ -42,6 +53,7 @@ struct AGNode {
     int     fused_pad;     /* matmul that consumed its padones parent virtually */
     float   sgd_lr;        /* > 0: value -= sgd_lr * grad as soon as the gradient is final */
     int     reduced_in_rule;   /* the rule that produced the gradient already reduced/applied it in chunks */
+    int     grad_is_seed;      /* grad is the caller's seed tensor, shared: replace, never write */
 };
 
 /* ---- construction ----------------------------------------------------------*/
@@ -55,7 +67,15 @@ static AGNode *node_make(Tensor *val, int requires_grad, int kind) {
     n->refcount = 1;
     return n;
 }
-static void node_link(AGNode *n, AGNode *p) { n->parents[n->nparents++] = ag_retain(p); }
+/* Forward-only mode (ttb_set_grad_enabled(0), the evaluation batches of
+ * tests/gate_mnist_mlp.py:74-80): a node keeps no link to its parents and asks for no gradient,
+ * so every activation is freed the moment the caller releases its node. */
+static void node_link(AGNode *n, AGNode *p) {
+    if (!g_tt.grad_enabled) { n->requires_grad = 0; return; }
+    n->parents[n->nparents++] = ag_retain(p);
+}
+extern "C" void ttb_set_grad_enabled(int on) { g_tt.grad_enabled = on ? 1 : 0; }
+extern "C" int ttb_grad_enabled(void) { return g_tt.grad_enabled; }
 
 extern "C" AGNode *ag_leaf(Tensor *t, int requires_grad) {
     if (!t) return nullptr;
@@ -95,6 +115,8 @@ extern "C" AGNode *ag_mulscalar(AGNode *a, float s) {
 }
 extern "C" AGNode *ag_relu(AGNode *a) {
     if (!a) return nullptr;
+    if (a->kind == OP_MATMUL && tt_is_deferred_matmul(a->val))      /* one GEMM, relu in its epilogue */
+        return unary_node(a, tt_deferred_matmul_relu(a->val), OP_RELU);
     return unary_node(a, tt_relu(a->val), OP_RELU);
 }
 extern "C" AGNode *ag_softmax(AGNode *a) {
@@ -117,29 +139,40 @@ extern "C" AGNode *ag_padones(AGNode *a) {
     return unary_node(a, v, OP_PADONES);
 }
 
+static int matmul_shapes_ok(const Tensor *av, const Tensor *bv) {
+    return av->ndim == 2 && bv->ndim == 2 && av->shape[1] == bv->shape[0] && av->shape[0] <= 0x7fffffffL &&
+           bv->shape[0] <= 0x7fffffffL && bv->shape[1] <= 0x7fffffffL;
+}
+
 extern "C" AGNode *ag_matmul(AGNode *a, AGNode *b) {
     if (!a || !b) return nullptr;
     const Tensor *av = a->val, *bv = b->val;
-    if (a->kind == OP_PADONES && g_tt.fuse_padones && av->ndim == 2 && bv->ndim == 2 &&
-        av->shape[1] == bv->shape[0] && av->shape[0] <= 0x7fffffffL && bv->shape[0] <= 0x7fffffffL &&
-        bv->shape[1] <= 0x7fffffffL) {
-        /* x.padones().matmul(w) = x * w[:K] + w[K]   (src/autograd.c:195-212 then :168-171) */
-        const Tensor *xv = a->parents[0]->val;
-        const float *px = tt_dev_ro(xv), *pw = tt_dev_ro(bv);
-        if (!px || !pw) return nullptr;
-        long shp[2] = {av->shape[0], bv->shape[1]};
-        Tensor *out = tt_new_uninit(shp, 2);
-        if (!out) return nullptr;
-        GemmArgs g;
-        memset(&g, 0, sizeof g);
-        g.M = (int)shp[0]; g.N = (int)shp[1]; g.K = (int)av->shape[1];
-        g.A = px; g.lda = xv->shape[1]; g.a_pad_ones = 1;
-        g.B = pw; g.ldb = g.N; g.C = TT(out)->dev; g.ldc = g.N;
-        if (tt_gemm(&g) != 0) { tt_release(out); return nullptr; }
+    if (a->kind == OP_PADONES && g_tt.fuse_padones && TT(av)->lazy_kind == TT_LAZY_PADONES && matmul_shapes_ok(av, bv)) {
+        /* x.padones().matmul(w) = x * w[:K] + w[K]   (src/autograd.c:195-212 then :168-171); x is the
+         * source the deferred padones value holds (the node has no parent link in forward-only mode) */
+        Tensor *xv = &TT(av)->lazy_src->pub;
+        Tensor *out;
+        if (g_tt.fuse_relu) {
+            out = tt_new_lazy_matmul(xv, b->val, 1);          /* launched by whoever consumes it */
+        } else {
+            const float *px = tt_dev_ro(xv), *pw = tt_dev_ro(bv);
+            if (!px || !pw) return nullptr;
+            long shp[2] = {av->shape[0], bv->shape[1]};
+            out = tt_new_uninit(shp, 2);
+            if (!out) return nullptr;
+            GemmArgs g;
+            memset(&g, 0, sizeof g);
+            g.M = (int)shp[0]; g.N = (int)shp[1]; g.K = (int)av->shape[1];
+            g.A = px; g.lda = xv->shape[1]; g.a_pad_ones = 1;
+            g.B = pw; g.ldb = g.N; g.C = TT(out)->dev; g.ldc = g.N;
+            if (tt_gemm(&g) != 0) { tt_release(out); return nullptr; }
+        }
         AGNode *n = binary_node(a, b, out, OP_MATMUL);
         if (n) n->fused_pad = 1;
         return n;
     }
+    if (g_tt.fuse_relu && matmul_shapes_ok(av, bv))
+        return binary_node(a, b, tt_new_lazy_matmul(a->val, b->val, 0), OP_MATMUL);
     return binary_node(a, b, tt_matmul_omp(av, bv, 12), OP_MATMUL);
 }
 
@@ -185,6 +218,7 @@ extern "C" void ag_zero_grad(AGNode *n) {
     if (!n || !n->grad) return;
     tt_release(n->grad);
     n->grad = nullptr;
+    n->grad_is_seed = 0;
 }
 
 /* ---- gradient accumulation (src/autograd.c:44-63) ---------------------------
@@ -247,6 +281,12 @@ static void param_grad_ready(AGNode *p, long off, long count) {
         g_tt.stream = keep;
         if (dist) tt_dist_note_comm_work();
     }
+    if (dist) {
+        /* the communication stream is still working on both payloads: a release before
+         * ttb_dist_join (ag_zero_grad, ag_release) must not recycle their blocks under it */
+        tt_mark_busy(p->grad, g_tt.comm_stream);
+        if (p->sgd_lr > 0.0f) tt_mark_busy(p->val, g_tt.comm_stream);
+    }
 }
 
 /* ---- backward rules ----------------------------------------------------------*/
@@ -269,13 +309,21 @@ static void bw_matmul(AGNode *n) {
         const int Kr = (int)x->val->shape[1];
         if (x->requires_grad) {               /* dX = dC * W[:K]^T, bypassing the padones node */
             const float *pw = tt_dev_ro(b->val);
+            /* x is a relu node and this product is all of its gradient: mask it here (the relu's
+             * output is the mask) and hand it to the relu's parent; the relu node's own rule then
+             * finds no gradient and does nothing (src/autograd.c:318-327 folded into :308-316) */
+            AGNode *z = (g_tt.fuse_relu && x->kind == OP_RELU && !x->grad && x->pending == 1 && a->pending == 1 &&
+                         x->nparents == 1 && x->parents[0]->requires_grad) ? x->parents[0] : nullptr;
+            const float *pm = z ? tt_dev_ro(x->val) : nullptr;
+            if (z && !pm) z = nullptr;
             int acc;
-            float *dst = pw ? grad_target(x, &acc) : nullptr;
+            float *dst = pw ? grad_target(z ? z : x, &acc) : nullptr;
             if (dst) {
                 memset(&g, 0, sizeof g);
                 g.tb = 1; g.M = M; g.N = Kr; g.K = N;
                 g.A = pg; g.lda = N; g.B = pw; g.ldb = N; g.C = dst; g.ldc = Kr;
                 g.accumulate = acc; g.rule = 1;
+                if (z) { g.mask = pm; g.ldmask = Kr; }
                 tt_gemm(&g);
             }
         }
@@ -345,7 +393,9 @@ static void bw_matmul(AGNode *n) {
 static void bw_relu(AGNode *n) {             /* src/autograd.c:318-327, fused with the += */
     AGNode *p = n->parents[0];
     if (!p->requires_grad) return;
-    const float *px = tt_dev_ro(p->val), *pg = tt_dev_ro(n->grad);
+    /* x > 0 exactly when relu(x) > 0: a pre-activation that was never stored is not produced for this */
+    const Tensor *m = tt_is_deferred_matmul(p->val) ? n->val : p->val;
+    const float *px = tt_dev_ro(m), *pg = tt_dev_ro(n->grad);
     if (!px || !pg) return;
     int acc;
     float *dst = grad_target(p, &acc);
@@ -522,12 +572,26 @@ static void run_backward(AGNode *out, const float *seed_host, const Tensor *seed
         free(ord.v);
         return;
     }
-    if (!out->grad) out->grad = tt_new_like(out->val, 0);
-    float *pd = out->grad ? tt_dev_rw(out->grad) : nullptr;
-    if (pd) {
+    /* the root's value is observable once the pass has run: a product still deferred is launched now */
+    if (tt_is_deferred_matmul(out->val)) tt_dev_ro(out->val);
+    /* d(out) is OVERWRITTEN by the seed (src/autograd.c:711-719).  A seed that already is a device
+     * tensor is shared instead of copied: nothing ever adds into the root's gradient (it has no
+     * consumer in its own graph), and a later pass replaces the shared tensor instead of writing it. */
+    if (out->grad && out->grad_is_seed) { tt_release(out->grad); out->grad = nullptr; out->grad_is_seed = 0; }
+    float *pd = nullptr;
+    if (seed_dev && !out->grad && out->nparents > 0 && !out->is_param && out->sgd_lr <= 0.0f && tt_dev_ro(seed_dev)) {
+        out->grad = tt_retain((Tensor *)seed_dev);
+        out->grad_is_seed = 1;
+    } else {
+        if (!out->grad) out->grad = tt_new_like(out->val, 0);
+        pd = out->grad ? tt_dev_rw(out->grad) : nullptr;
+    }
+    if (pd || out->grad_is_seed) {
         const long numel = out->val->numel;
         int seeded = 1;
-        if (seed_host) {
+        if (out->grad_is_seed) {
+            /* shared */
+        } else if (seed_host) {
             seeded = tt_cuda_ok(cudaMemcpyAsync(pd, seed_host, sizeof(float) * (size_t)numel,
                                                 cudaMemcpyHostToDevice, g_tt.stream), "cudaMemcpyAsync(seed)");
         } else if (seed_dev) {

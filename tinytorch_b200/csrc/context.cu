@@ -12,7 +12,7 @@
 #include <unordered_map>
 #include <vector>
 
-TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, 0, 0};    /* -1: take the setting from the environment */
+TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, -1, 1, 0, 0};    /* -1: take the setting from the environment */
 
 static char g_err[512] = "";
 
@@ -78,6 +78,7 @@ static int ctx_open(int device) {
     }
     if (g_tt.gemm_path < 0) g_tt.gemm_path = env_int("TT_GEMM_PATH", 0);
     if (g_tt.fuse_padones < 0) g_tt.fuse_padones = env_int("TT_FUSE_PADONES", 1);
+    if (g_tt.fuse_relu < 0) g_tt.fuse_relu = env_int("TT_FUSE_RELU", 1);
     g_tt.ready = 1;
     return 0;
 }
@@ -176,6 +177,22 @@ void tt_dev_free(void *p) {
     cudaFreeAsync(p, g_tt.stream);
 }
 
+/* Device memory as the driver and the stream-ordered pool see it: {free bytes on the GPU, bytes the
+ * pool has reserved from the driver, bytes of the pool handed out}.  Equal before and after a call
+ * means the call neither went to the driver nor took a block from the pool. */
+extern "C" int ttb_mem_info(unsigned long long out[3]) {
+    if (!out || tt_ctx_init() != 0) return -1;
+    size_t free_b = 0, total_b = 0;
+    if (!tt_cuda_ok(cudaMemGetInfo(&free_b, &total_b), "cudaMemGetInfo")) return -1;
+    cudaMemPool_t pool;
+    unsigned long long reserved = 0, used = 0;
+    if (!tt_cuda_ok(cudaDeviceGetDefaultMemPool(&pool, g_tt.device), "cudaDeviceGetDefaultMemPool") ||
+        !tt_cuda_ok(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &reserved), "cudaMemPoolGetAttribute") ||
+        !tt_cuda_ok(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &used), "cudaMemPoolGetAttribute")) return -1;
+    out[0] = (unsigned long long)free_b; out[1] = reserved; out[2] = used;
+    return 0;
+}
+
 extern "C" void *ttb_pinned_alloc(size_t bytes) {
     if (tt_ctx_init() != 0) return nullptr;
     void *p = nullptr;
@@ -210,7 +227,7 @@ static TracePair *g_pairs = nullptr;
 static long g_npairs = 0, g_cap_pairs = 0, g_made_pairs = 0;
 
 extern "C" void ttb_trace_enable(int on) { g_tt.trace = on ? 1 : 0; }
-extern "C" void ttb_trace_reset(void) { g_npairs = 0; }
+extern "C" void ttb_trace_reset(void) { g_npairs = 0; tt_dist_trace_reset(); }
 
 void tt_trace_begin(int kind) {
     if (!g_tt.trace) return;

@@ -23,6 +23,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <vector>
+
 /* The handful of NCCL declarations this file needs (public API, nccl.h). */
 typedef struct ncclComm *ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
@@ -101,8 +103,12 @@ extern "C" int ttb_dist_init(int rank, int world, const char id_in[128]) {
      * (gemm_tc.cu, TT_TC_FIT); NCCL is then held to the CTAs that fit there, unless the caller has
      * set NCCL_MAX_CTAS.  Measured together: 8 GPUs 2.65 -> 2.53 ms per step; either one alone loses. */
     {
+        int fit = 1, from = 4;
+#ifdef TT_TUNING
         const char *f = getenv("TT_TC_FIT"), *fw = getenv("TT_TC_FIT_WORLD");
-        const int fit = (f && *f) ? atoi(f) : 1, from = (fw && *fw) ? atoi(fw) : 4;
+        if (f && *f) fit = atoi(f);
+        if (fw && *fw) from = atoi(fw);
+#endif
         if (fit && world >= from) setenv("NCCL_MAX_CTAS", "16", 0);
     }
     ncclUniqueId id;
@@ -124,31 +130,54 @@ int tt_dist_active(void) { return g_comm != nullptr && g_world > 1; }
  * ttb_dist_join must order the compute stream after it. */
 void tt_dist_note_comm_work(void) { g_inflight++; }
 
-/* Sum `t` over all ranks in place.  Ordered after everything already on the
- * compute stream; runs on the communication stream. */
+/* ---- per-collective timing (while ttb_trace_enable is on) ---------------------------------
+ * Every reduction is bracketed by an event pair on the communication stream, and every
+ * ttb_dist_join by one event at the compute stream's tail (before it is made to wait) and
+ * one at the communication stream's tail: the second minus the first is the time the
+ * collectives and the updates behind them were NOT hidden by compute in that step. */
+struct CommPair { cudaEvent_t a, b; double bytes; };
+static std::vector<CommPair> g_cpairs, g_jpairs;      /* event pools, reused across resets */
+static size_t g_ncpairs = 0, g_njpairs = 0;
+
+void tt_dist_trace_reset(void) { g_ncpairs = 0; g_njpairs = 0; }
+
+static CommPair *pair_from(std::vector<CommPair> &pool, size_t &used) {
+    if (used == pool.size()) {
+        CommPair c = {nullptr, nullptr, 0.0};
+        if (cudaEventCreate(&c.a) != cudaSuccess || cudaEventCreate(&c.b) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        pool.push_back(c);
+    }
+    return &pool[used++];
+}
+
+/* Sum count floats at p over all ranks in place: ordered after everything already on the
+ * compute stream, runs on the communication stream. */
+static int reduce_on_comm_stream(float *p, size_t count) {
+    if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
+        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
+    CommPair *tp = g_tt.trace ? pair_from(g_cpairs, g_ncpairs) : nullptr;
+    if (tp) { tp->bytes = 4.0 * (double)count; cudaEventRecord(tp->a, g_tt.comm_stream); }
+    int rc = 0;
+    if (tt_peer_usable(p, count)) {
+        if (tt_peer_allreduce(p, count, g_tt.comm_stream) != 0) rc = -1;
+    } else if (!nccl_ok(nccl.AllReduce(p, p, count, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream), "ncclAllReduce")) rc = -1;
+    if (tp) cudaEventRecord(tp->b, g_tt.comm_stream);
+    if (rc == 0) g_inflight++;
+    return rc;
+}
+
 int tt_dist_allreduce_async(Tensor *t) {
     if (!tt_dist_active()) return 0;
     float *p = tt_dev_rw(t);
     if (!p) return -1;
-    if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
-        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
-    if (tt_peer_usable(p, (size_t)t->numel)) {
-        if (tt_peer_allreduce(p, (size_t)t->numel, g_tt.comm_stream) != 0) return -1;
-    } else if (!nccl_ok(nccl.AllReduce(p, p, (size_t)t->numel, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream),
-                        "ncclAllReduce")) return -1;
-    g_inflight++;
+    if (reduce_on_comm_stream(p, (size_t)t->numel) != 0) return -1;
+    tt_mark_busy(t, g_tt.comm_stream);
     return 0;
 }
 
 int tt_dist_allreduce_range(float *p, size_t count) {
     if (!tt_dist_active() || !count) return 0;
-    if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
-        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
-    if (tt_peer_usable(p, count)) {
-        if (tt_peer_allreduce(p, count, g_tt.comm_stream) != 0) return -1;
-    } else if (!nccl_ok(nccl.AllReduce(p, p, count, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream), "ncclAllReduce")) return -1;
-    g_inflight++;
-    return 0;
+    return reduce_on_comm_stream(p, count);
 }
 
 extern "C" int ttb_dist_allreduce(Tensor *t) {
@@ -156,10 +185,38 @@ extern "C" int ttb_dist_allreduce(Tensor *t) {
     return tt_dist_allreduce_async(t);
 }
 
+/* Sums since the last ttb_trace_reset: {collectives, bytes reduced, ms inside collectives (event
+ * pairs on the communication stream, waiting for the slowest rank included), joins, exposed ms
+ * (communication stream's tail minus compute stream's tail at each join, when positive), longest
+ * collective in ms}.  Waits for both streams. */
+extern "C" int ttb_dist_comm_read(double out[6]) {
+    if (!out || g_tt.ready != 1) return -1;
+    if (!tt_cuda_ok(cudaStreamSynchronize(g_tt.stream), "cudaStreamSynchronize") ||
+        !tt_cuda_ok(cudaStreamSynchronize(g_tt.comm_stream), "cudaStreamSynchronize(comm)")) return -1;
+    for (int i = 0; i < 6; i++) out[i] = 0.0;
+    for (size_t i = 0; i < g_ncpairs; i++) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, g_cpairs[i].a, g_cpairs[i].b) != cudaSuccess) { cudaGetLastError(); continue; }
+        out[0] += 1.0; out[1] += g_cpairs[i].bytes; out[2] += ms;
+        if (ms > out[5]) out[5] = ms;
+    }
+    for (size_t i = 0; i < g_njpairs; i++) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, g_jpairs[i].a, g_jpairs[i].b) != cudaSuccess) { cudaGetLastError(); continue; }
+        out[3] += 1.0;
+        if (ms > 0.0f) out[4] += ms;
+    }
+    return 0;
+}
+
 /* Make the compute stream wait for every reduction enqueued so far. */
 extern "C" int ttb_dist_join(void) {
     if (g_comm == nullptr && !g_inflight) return 0;
     if (g_inflight) {
+        if (g_tt.trace) {
+            CommPair *jp = pair_from(g_jpairs, g_njpairs);
+            if (jp) { cudaEventRecord(jp->a, g_tt.stream); cudaEventRecord(jp->b, g_tt.comm_stream); }
+        }
         if (!tt_cuda_ok(cudaEventRecord(g_ev_done, g_tt.comm_stream), "cudaEventRecord") ||
             !tt_cuda_ok(cudaStreamWaitEvent(g_tt.stream, g_ev_done, 0), "cudaStreamWaitEvent")) return -1;
         g_inflight = 0;

@@ -44,6 +44,8 @@ struct SimtParams {
     const float *B; long ldb;
     float *C; long ldc;
     int accumulate;
+    int relu;
+    const float *mask; long ldmask;
     int a_pad_ones;
     int all_edge;
     int mfull, nfull;      /* extent of the register-tile region (MODE_FWD) */
@@ -124,6 +126,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(SimtParams p) {
             int gi = m0 + ty * 4 + i, gj = n0 + tx * 4 + j;
             if (gi >= p.M || gj >= p.N) continue;
             float r = acc[i][j];
+            if (p.relu) r = r > 0.0f ? r : 0.0f;
+            if (p.mask) r = p.mask[(long)gi * p.ldmask + gj] > 0.0f ? r : 0.0f;
             float *c = p.C + (long)gi * p.ldc + gj;
             *c = p.accumulate ? *c + r : r;
         }
@@ -136,6 +140,7 @@ int gemm_simt(const GemmArgs *g) {
     p.ta = g->ta; p.tb = g->tb; p.M = g->M; p.N = g->N; p.K = g->K;
     p.A = g->A; p.lda = g->lda; p.B = g->B; p.ldb = g->ldb; p.C = g->C; p.ldc = g->ldc;
     p.accumulate = g->accumulate;
+    p.relu = g->relu; p.mask = g->mask; p.ldmask = g->ldmask;
     p.a_pad_ones = a_pad_ones;
     p.all_edge = (mode_hint == 2);
     p.mfull = (g->M / 6) * 6;

@@ -177,13 +177,26 @@ __device__ __forceinline__ float split_lo(float x) {
     return fabsf(x) == INFINITY ? 0.0f : lo;   /* keep Inf an Inf instead of Inf - Inf */
 }
 
+/* The one-pass and no-split modes exist for timing experiments only and give wrong or
+ * TF32-grade numbers; a default build has neither (compile with -DTT_TUNING to get them,
+ * together with the TT_TC_* environment knobs). */
+#ifdef TT_TUNING
+#define TC_FULL_SPLIT(p) ((p).passes == 3)
+#define TC_MAKE_LO(p) ((p).passes == 3 && !(p).nosplit)
+#else
+#define TC_FULL_SPLIT(p) true
+#define TC_MAKE_LO(p) true
+#endif
+
 struct TcParams {
     int M, N, K;
     float *C; long ldc;
     const float *bias;
     int accumulate;
-    int passes;              /* 3 = full split, 1 = hi*hi only (bring-up aid) */
-    int nosplit;             /* tuning aid: issue the three MMAs but skip producing the lo tiles (wrong numbers) */
+    int relu;                /* epilogue: v = v > 0 ? v : 0 after the bias */
+    const float *mask; long ldmask;   /* epilogue: v = mask[m, n] > 0 ? v : 0 (gradient mask of a relu, from its output) */
+    int passes;              /* 3 = full split; TT_TUNING builds only: 1 = hi*hi only (bring-up aid, TF32-grade numbers) */
+    int nosplit;             /* TT_TUNING builds only: issue the three MMAs but skip producing the lo tiles (wrong numbers) */
     int noprefetch;          /* no L2 prefetch ahead of the loads (the pair kernel runs 5-20 % faster without) */
     int a_3d, b_3d;          /* MN-major operand described by a rank-3 map: one TMA per tile instead of one per 32 columns */
     /* Split-K: the reduction is cut into `splits` slices of kb_per_split K blocks; slice s of a tile
@@ -200,6 +213,56 @@ struct TcParams {
     float *tail_partial;
     uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
 };
+
+/* What an epilogue thread needs to finish one output row: where the row lives, and the
+ * elementwise steps fused behind the product (bias, relu, gradient mask, accumulate). */
+struct EpiRow {
+    float *crow;             /* crow[n] is column n of this thread's row of the destination */
+    const float *bias;       /* per column, or NULL */
+    const float *mrow;       /* mrow[n] > 0 keeps column n, or NULL */
+    int accumulate, relu;
+    bool vec_ok;             /* destination (and mask) rows allow 128-bit accesses */
+};
+/* Store 32 consecutive columns [gc, gc+32) of one accumulator row. */
+__device__ __forceinline__ void epi_store32(const uint32_t (&r)[32], int gc, int N, const EpiRow &e) {
+    if (e.vec_ok && gc + 32 <= N) {
+        #pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            if (e.bias) {
+                v.x += e.bias[gc + j]; v.y += e.bias[gc + j + 1];
+                v.z += e.bias[gc + j + 2]; v.w += e.bias[gc + j + 3];
+            }
+            if (e.relu) {
+                v.x = v.x > 0.0f ? v.x : 0.0f; v.y = v.y > 0.0f ? v.y : 0.0f;
+                v.z = v.z > 0.0f ? v.z : 0.0f; v.w = v.w > 0.0f ? v.w : 0.0f;
+            }
+            if (e.mrow) {
+                const float4 k = *(const float4 *)(e.mrow + gc + j);
+                v.x = k.x > 0.0f ? v.x : 0.0f; v.y = k.y > 0.0f ? v.y : 0.0f;
+                v.z = k.z > 0.0f ? v.z : 0.0f; v.w = k.w > 0.0f ? v.w : 0.0f;
+            }
+            if (e.accumulate) {
+                const float4 o = *(const float4 *)(e.crow + gc + j);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+            }
+            *(float4 *)(e.crow + gc + j) = v;
+        }
+    } else {
+        #pragma unroll
+        for (int j = 0; j < 32; j++) {
+            if (gc + j < N) {
+                float v = __uint_as_float(r[j]);
+                if (e.bias) v += e.bias[gc + j];
+                if (e.relu) v = v > 0.0f ? v : 0.0f;
+                if (e.mrow) v = e.mrow[gc + j] > 0.0f ? v : 0.0f;
+                if (e.accumulate) v += e.crow[gc + j];
+                e.crow[gc + j] = v;
+            }
+        }
+    }
+}
 
 template <int A_MN, int B_MN, int BN, int BK, int STAGES, int SPLIT_ACC>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -384,7 +447,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const uint64_t da_hi = make_desc<A_MN, BK>(a_hi + a_off);
                         const uint64_t db_hi = make_desc<B_MN, BK>(b_hi + b_off);
                         const uint32_t first = (kb > kb0 || ks > 0) ? 1u : 0u;
-                        if (p.passes == 3) {
+                        if (TC_FULL_SPLIT(p)) {
                             const uint64_t da_lo = make_desc<A_MN, BK>(a_lo + a_off);
                             const uint64_t db_lo = make_desc<B_MN, BK>(b_lo + b_off);
                             tc_mma_tf32(d_corr, da_lo, db_hi, IDESC, first);
@@ -412,7 +475,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             decode(it, m0, n0, kb0, kb1, split);
             for (int kb = kb0; kb < kb1; kb++) {
                 if (!mbar_wait_warp(bar_full + 8 * s, ph, abort_flag, p.status, 1)) { ok = false; break; }
-                if (p.passes == 3 && !p.nosplit) {
+                if (TC_MAKE_LO(p)) {
                     const uint8_t *hi = smem_gen + s * STAGE_BYTES;
                     #pragma unroll 4
                     for (uint32_t c = st_tid; c < HI_BYTES / 16; c += TC_SPLIT_THREADS) {
@@ -441,26 +504,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool tail = p.tail_tiles && it >= full_tiles;
             const bool sliced = tail || p.splits > 1;
             const long ldc = tail ? (long)BN : (sliced ? (long)p.N : p.ldc);
-            const float *bias = sliced ? nullptr : p.bias;
-            const int accumulate = sliced ? 0 : p.accumulate;
             const int row = m0 + q * 32 + lane;
-            float *cbase, *crow;                       /* crow[n] addresses column n of this thread's row */
+            float *cbase;
+            EpiRow e;
+            e.bias = sliced ? nullptr : p.bias;
+            e.accumulate = sliced ? 0 : p.accumulate;
+            e.relu = sliced ? 0 : p.relu;
+            e.mrow = (sliced || !p.mask) ? nullptr : p.mask + (long)row * p.ldmask;
             if (tail) {
                 const int j = it - full_tiles - split * p.tail_tiles;
                 cbase = p.tail_partial + ((long)split * p.tail_tiles + j) * (TC_BM * BN);
-                crow = cbase + (long)(q * 32 + lane) * BN - n0;
+                e.crow = cbase + (long)(q * 32 + lane) * BN - n0;
             } else {
                 cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
-                crow = cbase + (long)row * ldc;
+                e.crow = cbase + (long)row * ldc;
             }
-            const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0);
+            e.vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0) &&
+                       (!e.mrow || (((p.ldmask & 3) == 0) && ((((uintptr_t)p.mask) & 15u) == 0)));
             if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5)) { ok = false; break; }   /* tcgen05.ld needs the whole warp */
             tc_fence_after();
             #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                if (SPLIT_ACC && p.passes == 3) {
+                if (SPLIT_ACC && TC_FULL_SPLIT(p)) {
                     uint32_t r2[32];
                     tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), r2);
                     tc_wait_ld();
@@ -475,34 +542,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
                 }
                 const int gc = n0 + c0;
-                if (row < p.M && gc < p.N) {
-                    if (vec_ok && gc + 32 <= p.N) {
-                        #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            if (bias) {
-                                v.x += bias[gc + j]; v.y += bias[gc + j + 1];
-                                v.z += bias[gc + j + 2]; v.w += bias[gc + j + 3];
-                            }
-                            if (accumulate) {
-                                float4 o = *(const float4 *)(crow + gc + j);
-                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                            }
-                            *(float4 *)(crow + gc + j) = v;
-                        }
-                    } else {
-                        #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (gc + j < p.N) {
-                                float v = __uint_as_float(r[j]);
-                                if (bias) v += bias[gc + j];
-                                if (accumulate) v += crow[gc + j];
-                                crow[gc + j] = v;
-                            }
-                        }
-                    }
-                }
+                if (row < p.M && gc < p.N) epi_store32(r, gc, p.N, e);
             }
             if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
         }
@@ -748,7 +788,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         const uint64_t da_hi = make_desc<A_MN, BK>(a_hi + a_off);
                         const uint64_t db_hi = make_desc<B_MN, BK>(b_hi + b_off);
                         const uint32_t first = (kb > kb0 || ks > 0) ? 1u : 0u;
-                        if (p.passes == 3) {
+                        if (TC_FULL_SPLIT(p)) {
                             const uint64_t da_lo = make_desc<A_MN, BK>(a_lo + a_off);
                             const uint64_t db_lo = make_desc<B_MN, BK>(b_lo + b_off);
                             tc2_mma_tf32(d_corr, da_lo, db_hi, IDESC, first);
@@ -776,7 +816,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             decode(it, m0, n0, kb0, kb1, split);
             for (int kb = kb0; kb < kb1; kb++) {
                 if (!mbar_wait_warp(bar_full + 8 * s, ph, abort_flag, p.status, 1)) { ok = false; break; }
-                if (p.passes == 3 && !p.nosplit) {
+                if (TC_MAKE_LO(p)) {
                     const uint8_t *hi = smem_gen + s * STAGE_BYTES;
                     #pragma unroll 4
                     for (uint32_t c = st_tid; c < HI_BYTES / 16; c += TC_SPLIT_THREADS) {
@@ -802,26 +842,30 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const bool tail = p.tail_tiles && it >= full_tiles;
             const bool sliced = tail || p.splits > 1;
             const long ldc = tail ? (long)BN : (sliced ? (long)p.N : p.ldc);
-            const float *bias = sliced ? nullptr : p.bias;
-            const int accumulate = sliced ? 0 : p.accumulate;
             const int row = m0 + (int)rank * TC_BM + q * 32 + lane;
-            float *cbase, *crow;                       /* crow[n] addresses column n of this thread's row */
+            float *cbase;
+            EpiRow e;
+            e.bias = sliced ? nullptr : p.bias;
+            e.accumulate = sliced ? 0 : p.accumulate;
+            e.relu = sliced ? 0 : p.relu;
+            e.mrow = (sliced || !p.mask) ? nullptr : p.mask + (long)row * p.ldmask;
             if (tail) {
                 const int j = it - full_tiles - split * p.tail_tiles;
                 cbase = p.tail_partial + ((long)split * p.tail_tiles + j) * (256 * BN);
-                crow = cbase + (long)((int)rank * TC_BM + q * 32 + lane) * BN - n0;
+                e.crow = cbase + (long)((int)rank * TC_BM + q * 32 + lane) * BN - n0;
             } else {
                 cbase = sliced ? p.partial + (long)split * p.M * p.N : p.C;
-                crow = cbase + (long)row * ldc;
+                e.crow = cbase + (long)row * ldc;
             }
-            const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0);
+            e.vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)cbase) & 15u) == 0) &&
+                       (!e.mrow || (((p.ldmask & 3) == 0) && ((((uintptr_t)p.mask) & 15u) == 0)));
             if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5)) { ok = false; break; }
             tc_fence_after();
             #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                if (SPLIT_ACC && p.passes == 3) {
+                if (SPLIT_ACC && TC_FULL_SPLIT(p)) {
                     uint32_t r2[32];
                     tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), r2);
                     tc_wait_ld();
@@ -835,31 +879,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (lane == 0) mbar_arrive_cluster(lead_tempty + 8 * acc);
                 }
                 const int gc = n0 + c0;
-                if (row < p.M && gc < p.N) {
-                    if (vec_ok && gc + 32 <= p.N) {
-                        #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            if (bias) { v.x += bias[gc + j]; v.y += bias[gc + j + 1]; v.z += bias[gc + j + 2]; v.w += bias[gc + j + 3]; }
-                            if (accumulate) {
-                                float4 o = *(const float4 *)(crow + gc + j);
-                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                            }
-                            *(float4 *)(crow + gc + j) = v;
-                        }
-                    } else {
-                        #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (gc + j < p.N) {
-                                float v = __uint_as_float(r[j]);
-                                if (bias) v += bias[gc + j];
-                                if (accumulate) v += crow[gc + j];
-                                crow[gc + j] = v;
-                            }
-                        }
-                    }
-                }
+                if (row < p.M && gc < p.N) epi_store32(r, gc, p.N, e);
             }
             if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
         }
@@ -874,10 +894,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
 }
 
-/* Second phase of split-K: C[m,n] (+)= bias[n] + sum over slices, slices added in order. */
+/* The elementwise steps fused behind a product, for the kernels that finish a sliced one. */
+struct EpiFused { const float *bias; int accumulate, relu; const float *mask; long ldmask; };
+
+/* Second phase of split-K: C[m,n] (+)= f(bias[n] + sum over slices), slices added in order. */
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, int splits, int M, int N,
-                                                             float *__restrict__ C, long ldc, const float *__restrict__ bias,
-                                                             int accumulate) {
+                                                             float *__restrict__ C, long ldc, EpiFused f) {
+    const float *__restrict__ bias = f.bias;
+    const int accumulate = f.accumulate;
     const long total = (long)M * N;
     const long stride = (long)gridDim.x * blockDim.x;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -885,20 +909,24 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
         float s = 0.0f;
         for (int k = 0; k < splits; k++) s += partial[(long)k * total + i];
         if (bias) s += bias[n];
+        if (f.relu) s = s > 0.0f ? s : 0.0f;
+        if (f.mask) s = f.mask[(long)m * f.ldmask + n] > 0.0f ? s : 0.0f;
         float *c = C + (long)m * ldc + n;
         *c = accumulate ? *c + s : s;
     }
 }
 
-/* Second phase of the tail split: for each tail tile, C (+)= bias + slices in order. */
+/* Second phase of the tail split: for each tail tile, C (+)= f(bias + slices in order). */
 __global__ void __launch_bounds__(256) tail_reduce_kernel(const float *__restrict__ partial, int splits, int tail_tiles,
                                                            int first_tile, int tiles_m, int BM, int BN, int M, int N,
-                                                           float *__restrict__ C, long ldc, const float *__restrict__ bias,
-                                                           int accumulate) {
+                                                           float *__restrict__ C, long ldc, EpiFused f) {
+    const float *__restrict__ bias = f.bias;
+    const int accumulate = f.accumulate;
     const int tile4 = BM * BN / 4, bn4 = BN / 4;
     const long total4 = (long)tail_tiles * tile4;
     const long stride = (long)gridDim.x * blockDim.x;
-    const bool vec_c = ((ldc & 3) == 0) && ((((uintptr_t)C) & 15u) == 0);
+    const bool vec_c = ((ldc & 3) == 0) && ((((uintptr_t)C) & 15u) == 0) &&
+                       (!f.mask || (((f.ldmask & 3) == 0) && ((((uintptr_t)f.mask) & 15u) == 0)));
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
         const int tj = (int)(i / tile4);
         const int rem = (int)(i - (long)tj * tile4);
@@ -914,6 +942,15 @@ __global__ void __launch_bounds__(256) tail_reduce_kernel(const float *__restric
         float *cp = C + (long)m * ldc + n;
         if (vec_c && n + 3 < N) {
             if (bias) { s.x += bias[n]; s.y += bias[n + 1]; s.z += bias[n + 2]; s.w += bias[n + 3]; }
+            if (f.relu) {
+                s.x = s.x > 0.0f ? s.x : 0.0f; s.y = s.y > 0.0f ? s.y : 0.0f;
+                s.z = s.z > 0.0f ? s.z : 0.0f; s.w = s.w > 0.0f ? s.w : 0.0f;
+            }
+            if (f.mask) {
+                const float4 k = *(const float4 *)(f.mask + (long)m * f.ldmask + n);
+                s.x = k.x > 0.0f ? s.x : 0.0f; s.y = k.y > 0.0f ? s.y : 0.0f;
+                s.z = k.z > 0.0f ? s.z : 0.0f; s.w = k.w > 0.0f ? s.w : 0.0f;
+            }
             if (accumulate) { const float4 o = *(const float4 *)cp; s.x = o.x + s.x; s.y = o.y + s.y; s.z = o.z + s.z; s.w = o.w + s.w; }
             *(float4 *)cp = s;
         } else {
@@ -921,6 +958,8 @@ __global__ void __launch_bounds__(256) tail_reduce_kernel(const float *__restric
             for (int j = 0; j < 4 && n + j < N; j++) {
                 float v = sv[j];
                 if (bias) v += bias[n + j];
+                if (f.relu) v = v > 0.0f ? v : 0.0f;
+                if (f.mask) v = f.mask[(long)m * f.ldmask + n + j] > 0.0f ? v : 0.0f;
                 cp[j] = accumulate ? cp[j] + v : v;
             }
         }
@@ -947,8 +986,10 @@ static int g_tc_fit_world = 4;       /* from this many ranks on (on two GPUs the
 static int g_tc_mn3d = 1;            /* TT_TC_MN3D=0: tuning aid, one TMA per 32 columns for MN-major tiles */
 static int g_tc_split_k = 1024;      /* reductions longer than this use the split accumulators */
 
-/* Tuning knobs from the environment (no GPU needed). */
+/* Tuning knobs from the environment (no GPU needed).  Only a -DTT_TUNING build reads them: several
+ * (one pass, no split) make the kernel produce wrong numbers and none belongs in a product build. */
 static void tc_read_env(void) {
+#ifdef TT_TUNING
     static bool done = false;
     if (done) return;
     done = true;
@@ -976,6 +1017,7 @@ static void tc_read_env(void) {
     if (e && *e) g_tc_force_bn = atoi(e);
     e = getenv("TT_TC_SPLIT_K");
     if (e && *e) g_tc_split_k = atoi(e);
+#endif
 }
 
 static int tc_setup(void) {
@@ -1008,9 +1050,32 @@ int gemm_tc_poll_status(void) {
     return 0;
 }
 
+/* Encoded tensor maps are kept: a training loop presents the same few (address, shape, pitch, box)
+ * combinations every step (the pool hands a layer's activations the same block each time), and an
+ * encode is a driver call.  Direct-mapped, 256 slots, keyed by everything that goes into the map. */
+struct MapKey { const float *base; long d0, d1, pitch; int b0, b1, b2, kind; };
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+static MapSlot g_maps[256];
+static bool map_key_eq(const MapKey &a, const MapKey &b) {
+    return a.base == b.base && a.d0 == b.d0 && a.d1 == b.d1 && a.pitch == b.pitch && a.b0 == b.b0 && a.b1 == b.b1 &&
+           a.b2 == b.b2 && a.kind == b.kind;
+}
+static MapSlot *map_slot(const MapKey &k, bool *hit) {
+    uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull;
+    h ^= (uint64_t)k.d0 * 0xC2B2AE3D27D4EB4Full + (uint64_t)k.d1 * 0x165667B19E3779F9ull + (uint64_t)k.pitch * 31 +
+         (uint64_t)(k.b0 * 131 + k.b1 * 17 + k.b2 * 7 + k.kind);
+    MapSlot *s = &g_maps[(h >> 32) & 255];
+    *hit = s->used && map_key_eq(s->key, k);
+    return s;
+}
+
 /* inner = contiguous extent, outer = number of rows, pitch in floats */
 static int encode_map(CUtensorMap *map, const float *base, long inner, long outer, long pitch, int box_inner, int box_outer,
                       int mn_major) {
+    const MapKey key = {base, inner, outer, pitch, box_inner, box_outer, 0, mn_major ? 1 : 0};
+    bool hit;
+    MapSlot *slot = map_slot(key, &hit);
+    if (hit) { *map = slot->map; return 0; }
     /* K-major boxes are box_inner*4 bytes wide: 128 -> SWIZZLE_128B, 64 -> SWIZZLE_64B */
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
@@ -1022,6 +1087,7 @@ static int encode_map(CUtensorMap *map, const float *base, long inner, long oute
                                    : (box_inner == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { tt_set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return -1; }
+    slot->key = key; slot->map = *map; slot->used = true;
     return 0;
 }
 
@@ -1030,6 +1096,10 @@ static int encode_map(CUtensorMap *map, const float *base, long inner, long oute
  * {32, 32, groups} then lands in shared memory group after group, 32 k-rows of 128 bytes
  * each -- the layout the kernel's MN-major descriptors expect -- with ONE copy per tile. */
 static int encode_map_mn3d(CUtensorMap *map, const float *base, long mn, long k, long pitch, int groups, int bk) {
+    const MapKey key = {base, mn, k, pitch, 32, bk, groups, 2};
+    bool hit;
+    MapSlot *slot = map_slot(key, &hit);
+    if (hit) { *map = slot->map; return 0; }
     cuuint64_t dims[3] = {32, (cuuint64_t)k, (cuuint64_t)(mn / 32)};
     cuuint64_t strides[2] = {(cuuint64_t)pitch * sizeof(float), 128};
     cuuint32_t box[3] = {32, (cuuint32_t)bk, (cuuint32_t)groups};
@@ -1037,7 +1107,9 @@ static int encode_map_mn3d(CUtensorMap *map, const float *base, long mn, long k,
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : -1;
+    if (r != CUDA_SUCCESS) return -1;
+    slot->key = key; slot->map = *map; slot->used = true;
+    return 0;
 }
 
 int gemm_tc_usable(const GemmArgs *g) {
@@ -1066,6 +1138,8 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     p.M = g->M; p.N = g->N; p.K = g->K; p.C = g->C; p.ldc = g->ldc; p.bias = g->bias;
     p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev; p.nosplit = g_tc_nosplit; p.noprefetch = g_tc_prefetch == 0;
     p.a_3d = a_3d; p.b_3d = b_3d;
+    p.relu = g->relu; p.mask = g->mask; p.ldmask = g->ldmask;
+    const EpiFused fused = {g->bias, g->accumulate, g->relu, g->mask, g->ldmask};
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
     p.tail_tiles = g_plan.tail_tiles; p.tail_splits = g_plan.tail_splits; p.tail_kb = g_plan.tail_kb;
     p.tail_partial = g_plan.tail_partial;
@@ -1082,13 +1156,13 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
         long blocks = (total4 + 255) / 256, cap = (long)g_tt.sm_count * 8;
         tail_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
             p.tail_partial, p.tail_splits, p.tail_tiles, plain_tiles - p.tail_tiles, tiles_m, TC_BM, BN, g->M, g->N,
-            g->C, g->ldc, g->bias, g->accumulate);
+            g->C, g->ldc, fused);
         g_tt.launches++;
     } else if (p.splits > 1) {
         long total = (long)g->M * g->N;
         long blocks = (total + 255) / 256, cap = (long)g_tt.sm_count * 8;
         splitk_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
-            p.partial, p.splits, g->M, g->N, g->C, g->ldc, g->bias, g->accumulate);
+            p.partial, p.splits, g->M, g->N, g->C, g->ldc, fused);
         g_tt.launches++;
     }
     tt_trace_end(TTB_K_GEMM_TC, 2.0 * (double)g->M * g->N * g->K);
@@ -1109,6 +1183,8 @@ static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUten
     p.M = g->M; p.N = g->N; p.K = g->K; p.C = g->C; p.ldc = g->ldc; p.bias = g->bias;
     p.accumulate = g->accumulate; p.passes = g_tc_passes; p.status = g_status_dev; p.nosplit = g_tc_nosplit; p.noprefetch = g_tc_prefetch != 1;
     p.a_3d = a_3d; p.b_3d = b_3d;
+    p.relu = g->relu; p.mask = g->mask; p.ldmask = g->ldmask;
+    const EpiFused fused = {g->bias, g->accumulate, g->relu, g->mask, g->ldmask};
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
     p.tail_tiles = g_plan.tail_tiles; p.tail_splits = g_plan.tail_splits; p.tail_kb = g_plan.tail_kb;
     p.tail_partial = g_plan.tail_partial;
@@ -1125,13 +1201,13 @@ static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUten
         long blocks = (total4 + 255) / 256, cap = (long)g_tt.sm_count * 8;
         tail_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
             p.tail_partial, p.tail_splits, p.tail_tiles, (int)plain_tiles - p.tail_tiles, tiles_m, 256, 256, g->M, g->N,
-            g->C, g->ldc, g->bias, g->accumulate);
+            g->C, g->ldc, fused);
         g_tt.launches++;
     } else if (p.splits > 1) {
         long total = (long)g->M * g->N;
         long blocks = (total + 255) / 256, cap = (long)g_tt.sm_count * 8;
         splitk_reduce_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, g_tt.stream>>>(
-            p.partial, p.splits, g->M, g->N, g->C, g->ldc, g->bias, g->accumulate);
+            p.partial, p.splits, g->M, g->N, g->C, g->ldc, fused);
         g_tt.launches++;
     }
     tt_trace_end(TTB_K_GEMM_TC, 2.0 * (double)g->M * g->N * g->K);

@@ -609,7 +609,7 @@ __global__ void __launch_bounds__(256) colsum_fused_kernel(const float *__restri
     }
     if (threadIdx.x == 0) g_colsum_tickets[blockIdx.x] = 0;      /* ready for the next launch */
 }
-void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate) {
+int k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate) {
     /* as many row slabs as give every SM its full set of resident blocks exactly once: a second,
      * nearly empty wave of blocks costs as much time as the first */
     static int per_sm = 0;
@@ -637,7 +637,7 @@ void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate)
         scratch_floats = scratch ? need : 0;
     }
     float *part = scratch;
-    if (!part) return;
+    if (!part) { tt_set_error("column sum: no scratch memory for %zu partial sums", need); return -1; }
     tt_trace_begin(TTB_K_REDUCE);
     dim3 grid(col_blocks, slabs);
     if (fused) {
@@ -647,23 +647,25 @@ void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate)
         LAUNCH(colsum_final_kernel, (N + TPB - 1) / TPB, TPB, 0, part, slabs, N, out, accumulate);
     }
     tt_trace_end(TTB_K_REDUCE, 4.0 * (double)M * N);
+    return 0;
 }
 
 /* ---- column sums for callers that must not allocate ----------------------------
  * Some hosts of this library cannot reach the device allocator when they need a
  * bias gradient: a process that handed every byte of device memory to its own
- * arena at start-up and forbids any other allocation afterwards, a latency-bound
- * loop in which an allocator call is not acceptable, or code that runs while a
- * stream is being recorded, where asking the driver for memory is an error.  For
- * them the partial sums live in a fixed array inside the library image instead
- * of in pool memory.  Every GPU that loads the library carries the array
+ * arena at start-up and forbids any other allocation afterwards, or a
+ * latency-bound loop in which an allocator call is not acceptable.  For them the
+ * partial sums live in a fixed array inside the library image instead of in pool
+ * memory.  Every GPU that loads the library carries the array
  * (TTB_COLSUM_STATIC_SLABS x TTB_COLSUM_STATIC_MAX_COLS floats = 2 MiB) until
  * the process exits.
  *
  * The array's name is only a stand-in on the host; what a kernel can use is the
  * address cudaGetSymbolAddress returns for it on the current device.  That
- * lookup is done here, once per device, on the first call made with that device
- * current -- so make the first call on a device before recording a stream.
+ * lookup is done here on the first call, for the one device the library runs on
+ * and with that device current (the launch goes to the library's stream, which
+ * belongs to that device, so a call made while another device is current is
+ * refused) -- make the first call before any stream capture is begun.
  * All calls share the one array.  Each call overwrites every partial it later
  * reads, so nothing has to be cleared; but two calls that run on the GPU at the
  * same time (different streams, or different host threads) would trample each
@@ -671,7 +673,7 @@ void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate)
 #define TTB_COLSUM_STATIC_SLABS 32
 #define TTB_COLSUM_STATIC_MAX_COLS 16384
 static __device__ __align__(256) float g_colsum_static[TTB_COLSUM_STATIC_SLABS * TTB_COLSUM_STATIC_MAX_COLS];
-static float *g_colsum_static_addr[64];        /* device address of the array, per device ordinal */
+static float *g_colsum_static_addr = nullptr;  /* device address of the array on the library's device */
 
 extern "C" int ttb_colsum_static(const float *g_dev, int rows, int cols, long ldg, float *out_dev, int accumulate) {
     if (!g_dev || !out_dev || rows <= 0 || cols <= 0 || ldg < cols || ldg > 0x7fffffffL) {
@@ -686,13 +688,16 @@ extern "C" int ttb_colsum_static(const float *g_dev, int rows, int cols, long ld
     if (tt_ctx_init() != 0) return -1;
     int dev = -1;
     if (!tt_cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return -1;
-    if (dev < 0 || dev >= 64) { tt_set_error("ttb_colsum_static: device ordinal %d not supported", dev); return -1; }
-    if (!g_colsum_static_addr[dev]) {
+    if (dev != g_tt.device) {
+        tt_set_error("ttb_colsum_static: device %d is current but the library runs on device %d", dev, g_tt.device);
+        return -1;
+    }
+    if (!g_colsum_static_addr) {
         float *addr = nullptr;
         if (!tt_cuda_ok(cudaGetSymbolAddress((void **)&addr, g_colsum_static), "cudaGetSymbolAddress") || !addr) return -1;
-        g_colsum_static_addr[dev] = addr;
+        g_colsum_static_addr = addr;
     }
-    float *part = g_colsum_static_addr[dev];
+    float *part = g_colsum_static_addr;
     int slabs = (rows + 63) / 64;
     if (slabs > TTB_COLSUM_STATIC_SLABS) slabs = TTB_COLSUM_STATIC_SLABS;
     int rows_per_slab = (rows + slabs - 1) / slabs;

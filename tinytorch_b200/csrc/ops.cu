@@ -77,8 +77,7 @@ int tt_gemm(const GemmArgs *g) {
         if (g->tb) return gemm_simt(g);
         if (gemm_tc(&core) != 0) return -1;
         /* last row of A^T is all ones: that row of C is the column sum of B */
-        k_colsum(g->B, g->K, g->N, (int)g->ldb, g->C + (long)core.M * g->ldc, g->accumulate);
-        return 0;
+        return k_colsum(g->B, g->K, g->N, (int)g->ldb, g->C + (long)core.M * g->ldc, g->accumulate);
     }
     return gemm_tc(&core);
 }
@@ -146,7 +145,10 @@ extern "C" Tensor *ttb_colsum(const Tensor *g) {
     long shp[1] = {g->shape[1]};
     Tensor *out = tt_new_uninit(shp, 1);
     if (!out) return nullptr;
-    k_colsum(pg, (int)g->shape[0], (int)g->shape[1], (int)g->shape[1], TT(out)->dev, 0);
+    if (k_colsum(pg, (int)g->shape[0], (int)g->shape[1], (int)g->shape[1], TT(out)->dev, 0) != 0) {
+        tt_release(out);
+        return nullptr;
+    }
     return out;
 }
 

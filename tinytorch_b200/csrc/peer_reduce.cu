@@ -23,9 +23,15 @@
  *   3. copy    r copies the chunks c != r from its result area into its gradient.
  * Every rank ends with bit-identical sums (each chunk is added once, by one rank).
  *
- * Every wait is bounded: when the limit passes, the kernel writes a code into a host-mapped
- * status word and stops waiting (its output is then wrong and ttb_dist_join reports the
- * failure); it never spins forever.  A launch may reuse the staging and result areas of the
+ * Every wait is bounded: when the limit passes (about two seconds; ttb_dist_set_wait_limit_ms
+ * changes it), the kernel writes a code into a host-mapped status word and stops waiting (its
+ * output is then wrong and ttb_dist_join reports the failure); it never spins forever.  A
+ * failure is sticky and spreads: the rank that gave up sets a poison word in its own flag
+ * block and in every peer's, every wait polls the waiter's poison words and every launch
+ * looks at them first, so a peer whose launches have fallen out of step with the rank that
+ * gave up reports the failure instead of passing its waits on stale flags and summing
+ * left-over staging data.  After a failure this process launches no further peer
+ * reductions (they return -1); the job has to tear the peer path down.  A launch may reuse the staging and result areas of the
  * previous one because a rank leaves a launch only after every peer has signalled the end
  * of its phase 2, and enters phase 2 only after every peer has entered the launch. */
 #include "tt_internal.h"
@@ -37,8 +43,10 @@
 #define PR_MAX_CTAS 64
 #define PR_THREADS 256
 #define PR_FLAG_WORDS (2 * PR_MAX_WORLD * PR_MAX_CTAS)
+#define PR_POISON_WORD PR_FLAG_WORDS             /* + rank: set by `rank` when one of its waits ran out */
 #define PR_FLAG_BYTES 16384                      /* flags block, padded */
 #define PR_WAIT_LIMIT (1u << 24)                 /* polls of ~128 ns: about two seconds */
+#define PR_POLLS_PER_MS 8192u
 
 struct PeerParams {
     float *g;                       /* this rank's gradient (or a contiguous part of it) */
@@ -51,7 +59,21 @@ struct PeerParams {
     float *result[PR_MAX_WORLD];    /* result area of rank p */
     unsigned *flags[PR_MAX_WORLD];  /* flag block of rank p */
     unsigned *status;               /* host-mapped: 0 = fine */
+    unsigned wait_limit;            /* polls before a wait gives up */
 };
+
+/* Has any rank (this one included) given up on a wait of this job? */
+__device__ __forceinline__ int pr_poisoned(const PeerParams &p) {
+    const volatile unsigned *mine = p.flags[p.rank] + PR_POISON_WORD;
+    int bad = 0;
+    for (int q = 0; q < p.world; q++) bad |= mine[q] != 0u;
+    return bad;
+}
+/* Tell everybody, this rank's later launches included, that this rank stopped waiting. */
+__device__ __forceinline__ void pr_poison_all(const PeerParams &p) {
+    for (int q = 0; q < p.world; q++) *(volatile unsigned *)(p.flags[q] + PR_POISON_WORD + p.rank) = 1u;
+    __threadfence_system();
+}
 
 __device__ __forceinline__ void pr_signal_and_wait(const PeerParams &p, int phase, int b, bool &ok, int *gave_up) {
     /* each thread orders its own peer stores before the flag that announces them */
@@ -65,8 +87,14 @@ __device__ __forceinline__ void pr_signal_and_wait(const PeerParams &p, int phas
             volatile unsigned *mine = p.flags[p.rank] + (phase * PR_MAX_WORLD + t) * PR_MAX_CTAS + b;
             unsigned n = 0;
             while ((int)(*mine - p.epoch) < 0) {
-                if (++n > PR_WAIT_LIMIT) {
+                if (++n > p.wait_limit) {
                     *(volatile unsigned *)p.status = 0x100u | ((unsigned)phase << 4) | (unsigned)t;
+                    *(volatile int *)gave_up = 1;
+                    pr_poison_all(p);
+                    break;
+                }
+                if ((n & 63u) == 0u && pr_poisoned(p)) {          /* somebody else gave up: so do we */
+                    *(volatile unsigned *)p.status = 0x200u | ((unsigned)phase << 4) | (unsigned)t;
                     *(volatile int *)gave_up = 1;
                     break;
                 }
@@ -89,8 +117,15 @@ __global__ void __launch_bounds__(PR_THREADS, 3) peer_allreduce_kernel(PeerParam
     float4 *g4 = (float4 *)p.g;
     bool ok = true;
     __shared__ int gave_up;
-    if (t == 0) gave_up = 0;
+    if (t == 0) {
+        gave_up = 0;
+        if (pr_poisoned(p)) {            /* a wait ran out earlier, here or on a peer: flags and staging are not to be trusted */
+            gave_up = 1;
+            *(volatile unsigned *)p.status = 0x300u | (unsigned)p.rank;
+        }
+    }
     __syncthreads();
+    if (gave_up) return;
 
     /* 1. push my part of every foreign chunk to its owner (four independent 128-bit loads per
      * thread and peer in flight: the stores are posted, the loads set the pace) */
@@ -160,7 +195,18 @@ static struct {
     char *base[PR_MAX_WORLD];        /* allocation of rank p as mapped here; [rank] is our own */
     unsigned epoch;
     unsigned *status_host, *status_dev;
+    unsigned wait_limit;             /* 0 = the default */
+    int failed;                      /* sticky: a bounded wait ran out in this job */
 } g_peer;
+
+/* How long a device-side wait on another rank may last before the kernel gives up and the
+ * failure is reported (default about two seconds).  For tests of the failure path and for
+ * jobs that want to learn of a dead peer sooner. */
+extern "C" int ttb_dist_set_wait_limit_ms(int ms) {
+    if (ms < 1 || ms > 60000) { tt_set_error("ttb_dist_set_wait_limit_ms: 1..60000"); return -1; }
+    g_peer.wait_limit = (unsigned)ms * PR_POLLS_PER_MS;
+    return 0;
+}
 
 static size_t pr_slot_floats(size_t max_floats, int world) {
     size_t c = (max_floats + world - 1) / world;
@@ -184,6 +230,7 @@ extern "C" int ttb_dist_peer_export(size_t max_floats, int world, char handle_ou
     const size_t bytes = pr_total_bytes(max_floats, world);
     if (!tt_cuda_ok(cudaMalloc(&p, bytes), "cudaMalloc(peer block)")) return -1;
     if (!tt_cuda_ok(cudaMemset(p, 0, PR_FLAG_BYTES), "cudaMemset(peer flags)")) { cudaFree(p); return -1; }
+    static_assert((PR_POISON_WORD + PR_MAX_WORLD) * sizeof(unsigned) <= PR_FLAG_BYTES, "flag block too small");
     cudaIpcMemHandle_t h;
     if (!tt_cuda_ok(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle")) { cudaFree(p); return -1; }
     static_assert(sizeof(h) == 64, "IPC handle size");
@@ -223,6 +270,7 @@ extern "C" int ttb_dist_peer_import(int rank, int world, const char *handles) {
     g_peer.rank = rank;
     g_peer.slot4 = (long)(pr_slot_floats(g_peer.max_floats, world) / 4);
     g_peer.epoch = 0;
+    g_peer.failed = 0;
     const char *e = getenv("TT_PEER_CTAS");
     g_peer.ctas = (e && *e) ? atoi(e) : 64;
     if (g_peer.ctas < 1) g_peer.ctas = 1;
@@ -237,6 +285,10 @@ int tt_peer_usable(const float *p, size_t count) {
 }
 
 int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream) {
+    if (g_peer.failed || tt_peer_poll_status()) {
+        tt_set_error("peer all-reduce: a bounded wait ran out earlier in this job; the peer path is shut");
+        return -1;
+    }
     PeerParams k;
     memset(&k, 0, sizeof k);
     const size_t padded_floats = (size_t)g_peer.slot4 * 4 * g_peer.world;
@@ -247,6 +299,7 @@ int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream) {
     k.rank = g_peer.rank; k.world = g_peer.world;
     k.epoch = ++g_peer.epoch;
     k.status = g_peer.status_dev;
+    k.wait_limit = g_peer.wait_limit ? g_peer.wait_limit : PR_WAIT_LIMIT;
     for (int q = 0; q < g_peer.world; q++) {
         k.flags[q] = (unsigned *)g_peer.base[q];
         k.stage[q] = (float *)(g_peer.base[q] + PR_FLAG_BYTES);
@@ -262,7 +315,13 @@ int tt_peer_poll_status(void) {
     if (!g_peer.status_host) return 0;
     unsigned v = *(volatile unsigned *)g_peer.status_host;
     if (v) {
-        tt_set_error("peer all-reduce: bounded wait expired (phase %u, waiting for rank %u)", (v >> 4) & 0xfu, v & 0xfu);
+        g_peer.failed = 1;
+        if ((v & 0xf00u) == 0x100u)
+            tt_set_error("peer all-reduce: bounded wait expired (phase %u, waiting for rank %u)", (v >> 4) & 0xfu, v & 0xfu);
+        else if ((v & 0xf00u) == 0x200u)
+            tt_set_error("peer all-reduce: another rank gave up on a wait (seen in phase %u while waiting for rank %u)", (v >> 4) & 0xfu, v & 0xfu);
+        else
+            tt_set_error("peer all-reduce: launched after a rank of the job had given up on a wait");
         return (int)v;
     }
     return 0;
@@ -270,15 +329,29 @@ int tt_peer_poll_status(void) {
 
 extern "C" int ttb_dist_peer_active(void) { return g_peer.active; }
 
-void tt_peer_finalize(void) {
-    if (g_peer.active || g_peer.base[0]) cudaDeviceSynchronize();
+/* Tear-down is in two halves because CUDA leaves it undefined to free an exported block while
+ * another process still has it open: first EVERY rank closes what it imported
+ * (ttb_dist_peer_close), then, after a rendezvous of all ranks, each rank frees its own block
+ * (ttb_dist_finalize).  tinytorch_b200.dist.finalize() does barrier / close / barrier / finalize. */
+extern "C" void ttb_dist_peer_close(void) {
+    if (!g_peer.active) return;
+    cudaDeviceSynchronize();
     for (int p = 0; p < PR_MAX_WORLD; p++) {
-        if (!g_peer.base[p]) continue;
-        if (g_peer.active && p != g_peer.rank) cudaIpcCloseMemHandle(g_peer.base[p]);
-        else cudaFree(g_peer.base[p]);
+        if (!g_peer.base[p] || p == g_peer.rank) continue;
+        cudaIpcCloseMemHandle(g_peer.base[p]);
         g_peer.base[p] = nullptr;
     }
+    /* our own block moves to the parking slot the export used; the peer kernel is off from here on */
+    char *own = g_peer.base[g_peer.rank];
+    g_peer.base[g_peer.rank] = nullptr;
+    g_peer.base[0] = own;
     g_peer.active = 0;
+}
+
+void tt_peer_finalize(void) {
+    if (g_peer.active) ttb_dist_peer_close();
+    if (g_peer.base[0]) { cudaDeviceSynchronize(); cudaFree(g_peer.base[0]); g_peer.base[0] = nullptr; }
     g_peer.epoch = 0;
+    g_peer.failed = 0;
     if (g_peer.status_host) *g_peer.status_host = 0;
 }

@@ -108,6 +108,46 @@ Tensor *tt_new_lazy_padones(Tensor *src) {
     return &t->pub;
 }
 
+/* A product that is not launched yet (see TT_LAZY_MATMUL).  Shapes are the caller's business. */
+Tensor *tt_new_lazy_matmul(Tensor *x, Tensor *w, int pad) {
+    if (!x || !w || x->ndim != 2 || w->ndim != 2) return nullptr;
+    long shp[2] = {x->shape[0], w->shape[1]};
+    long numel = checked_numel(shp, 2);
+    if (numel < 0) return nullptr;
+    TTensor *t = record_new(shp, 2, numel);
+    if (!t) return nullptr;
+    t->lazy_kind = TT_LAZY_MATMUL;
+    t->lazy_pad = pad ? 1 : 0;
+    t->lazy_src = TT(tt_retain(x));
+    t->lazy_src2 = TT(tt_retain(w));
+    return &t->pub;
+}
+
+int tt_is_deferred_matmul(const Tensor *t) { return t && TT(t)->lazy_kind == TT_LAZY_MATMUL; }
+
+/* Launch the product of a TT_LAZY_MATMUL tensor into dst[M,N]. */
+static int run_deferred_matmul(const TTensor *t, float *dst, int relu) {
+    const Tensor *x = &t->lazy_src->pub, *w = &t->lazy_src2->pub;
+    const float *px = tt_dev_ro(x), *pw = tt_dev_ro(w);
+    if (!px || !pw) return -1;
+    GemmArgs g;
+    memset(&g, 0, sizeof g);
+    g.M = (int)t->pub.shape[0]; g.N = (int)t->pub.shape[1]; g.K = (int)w->shape[0];
+    g.A = px; g.lda = x->shape[1]; g.a_pad_ones = t->lazy_pad;
+    g.B = pw; g.ldb = g.N; g.C = dst; g.ldc = g.N;
+    g.relu = relu;
+    return tt_gemm(&g);
+}
+
+Tensor *tt_deferred_matmul_relu(const Tensor *ct) {
+    const TTensor *t = TT(ct);
+    if (!t || t->lazy_kind != TT_LAZY_MATMUL) return nullptr;
+    Tensor *out = tt_new_uninit(t->pub.shape, 2);
+    if (!out) return nullptr;
+    if (run_deferred_matmul(t, TT(out)->dev, 1) != 0) { tt_release(out); return nullptr; }
+    return out;
+}
+
 extern "C" Tensor *tt_retain(Tensor *t) {
     if (!t) return nullptr;
     t->refcount++;
@@ -122,21 +162,45 @@ extern "C" void tt_release(Tensor *t) {
         if (x->ready_pending && g_tt.ready == 1) cudaStreamWaitEvent(g_tt.stream, x->ready, 0);   /* the free is stream-ordered */
         cudaEventDestroy(x->ready);
     }
+    if (x->busy) {
+        /* a download, reduction or fused update on another stream may still be using the block:
+         * whoever gets it next (the free is ordered on the compute stream) comes after that work */
+        if (x->busy_pending && g_tt.ready == 1) cudaStreamWaitEvent(g_tt.stream, x->busy, 0);
+        cudaEventDestroy(x->busy);
+    }
     if (x->dev) tt_dev_free(x->dev);
     if (x->lazy_src) tt_release(&x->lazy_src->pub);
+    if (x->lazy_src2) tt_release(&x->lazy_src2->pub);
     record_free(x);
+}
+
+void tt_mark_busy(Tensor *ct, cudaStream_t s) {
+    TTensor *t = TT(ct);
+    if (!t || g_tt.ready != 1) return;
+    if (!t->busy && cudaEventCreateWithFlags(&t->busy, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        t->busy = nullptr;
+        cudaStreamSynchronize(s);            /* no event to be had: fall back to waiting here */
+        return;
+    }
+    if (cudaEventRecord(t->busy, s) == cudaSuccess) t->busy_pending = 1;
 }
 
 /* Produce a deferred payload. */
 static int materialise(TTensor *t) {
     if (t->lazy_kind == TT_LAZY_NONE) return 1;
-    t->dev = (float *)tt_dev_alloc(sizeof(float) * (size_t)t->pub.numel);
-    if (!t->dev) return 0;
+    float *dev = (float *)tt_dev_alloc(sizeof(float) * (size_t)t->pub.numel);
+    if (!dev) return 0;
     if (t->lazy_kind == TT_LAZY_PADONES) {
         const float *src = tt_dev_ro(&t->lazy_src->pub);
-        if (!src) return 0;
-        k_padones(t->dev, src, (int)t->lazy_src->pub.shape[0], (int)t->lazy_src->pub.shape[1]);
+        if (!src) { tt_dev_free(dev); return 0; }     /* stays deferred; nothing is kept */
+        k_padones(dev, src, (int)t->lazy_src->pub.shape[0], (int)t->lazy_src->pub.shape[1]);
+    } else if (t->lazy_kind == TT_LAZY_MATMUL) {
+        if (run_deferred_matmul(t, dev, 0) != 0) { tt_dev_free(dev); return 0; }
+        tt_release(&t->lazy_src2->pub);
+        t->lazy_src2 = nullptr;
     }
+    t->dev = dev;
     tt_release(&t->lazy_src->pub);
     t->lazy_src = nullptr;
     t->lazy_kind = TT_LAZY_NONE;
@@ -214,6 +278,7 @@ extern "C" int ttb_download_async(const Tensor *src, float *dst) {
         !tt_cuda_ok(cudaMemcpyAsync(dst, p, sizeof(float) * (size_t)t->pub.numel, cudaMemcpyDeviceToHost,
                                     g_tt.copy_stream), "cudaMemcpyAsync(D2H)"))
         return -1;
+    tt_mark_busy(&t->pub, g_tt.copy_stream);      /* src may be released before ttb_download_wait */
     return 0;
 }
 extern "C" int ttb_download_wait(void) {

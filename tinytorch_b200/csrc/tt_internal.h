@@ -12,7 +12,11 @@
 
 /* ---- tensor record --------------------------------------------------------
  * The public struct comes first, so a Tensor* is also a TTensor*. */
-enum { TT_LAZY_NONE = 0, TT_LAZY_PADONES = 1 };
+/* TT_LAZY_PADONES: [M,K] -> [M,K+1] with a ones column, from lazy_src.
+ * TT_LAZY_MATMUL:  lazy_src * lazy_src2 (lazy_pad: lazy_src carries a virtual ones column, so the
+ *                  last row of lazy_src2 is added to every row), not launched yet: the builder that
+ *                  consumes it may fuse its own step into the product's epilogue instead. */
+enum { TT_LAZY_NONE = 0, TT_LAZY_PADONES = 1, TT_LAZY_MATMUL = 2 };
 
 typedef struct TTensor {
     Tensor  pub;
@@ -22,8 +26,12 @@ typedef struct TTensor {
     uint8_t host_exposed;  /* tt_data() handed the mirror out since the last upload */
     uint8_t lazy_kind;     /* payload not produced yet: TT_LAZY_* */
     struct TTensor *lazy_src;   /* retained source of a deferred payload */
+    struct TTensor *lazy_src2;  /* second retained source (TT_LAZY_MATMUL: the right-hand operand) */
+    uint8_t lazy_pad;           /* TT_LAZY_MATMUL: lazy_src has a virtual ones column */
     cudaEvent_t ready;     /* upload on the copy stream that the next device use must wait for */
     uint8_t ready_pending;
+    cudaEvent_t busy;      /* last use on another stream (download, all-reduce, fused update): release waits for it */
+    uint8_t busy_pending;
 } TTensor;
 
 static inline TTensor *TT(const Tensor *t) { return (TTensor *)t; }
@@ -39,6 +47,8 @@ typedef struct TTContext {
     cudaStream_t copy_stream;  /* asynchronous input uploads */
     int          gemm_path;    /* 0 auto, 1 tensor core, 2 exact fp32 */
     int          fuse_padones; /* fold padones into the adjoining GEMM */
+    int          fuse_relu;    /* fold relu and its gradient mask into the adjoining GEMMs' epilogues */
+    int          grad_enabled; /* 0: builders record no graph (forward-only / evaluation batches) */
     int          trace;
     long         launches;
 } TTContext;
@@ -57,6 +67,13 @@ Tensor *tt_new_like(const Tensor *a, int zero);
 float  *tt_dev_ro(const Tensor *t);            /* device pointer for reading (uploads / materialises) */
 float  *tt_dev_rw(Tensor *t);                  /* device pointer for writing; mirror becomes stale */
 Tensor *tt_new_lazy_padones(Tensor *src);      /* [M,K] -> [M,K+1], produced on first use */
+Tensor *tt_new_lazy_matmul(Tensor *x, Tensor *w, int pad);   /* x[M,K] (pad: virtual ones column) times w, produced on first use */
+int     tt_is_deferred_matmul(const Tensor *t);   /* a TT_LAZY_MATMUL tensor whose product has not been launched */
+/* The deferred product of `t` with a relu fused into its epilogue, as a new tensor; t stays deferred. */
+Tensor *tt_deferred_matmul_relu(const Tensor *t);
+/* The payload is being read or written on `s` (not the compute stream): its block must not be
+ * handed to another allocation before that work has finished.  tt_release orders the free after it. */
+void    tt_mark_busy(Tensor *t, cudaStream_t s);
 
 /* Tracing (context.cu): bracket a launch of class `kind`. */
 void tt_trace_begin(int kind);
@@ -80,7 +97,7 @@ void k_softmax_bwd(float *dx, const float *s, const float *g, long rows, int N);
 void k_softmax_xent(const float *logits, const float *labels, long rows, int N,
                     float scale, float *dlogits, float *row_loss);
 void k_mean(const float *x, long n, float *out);               /* out[0] = sum(x)/n */
-void k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate);
+int  k_colsum(const float *g, int M, int N, int ldg, float *out, int accumulate);   /* 0, or -1 when its scratch cannot be had */
 void k_sgd(float *w, const float *g, float lr, long n);
 void k_sgd_momentum(float *w, float *v, const float *g, float lr, float mu, long n);
 void k_adam(float *w, float *m, float *v, const float *g, float lr_t, float b1,
@@ -127,6 +144,13 @@ typedef struct GemmArgs {
     /* Which reference loop the exact-fp32 path reproduces bit for bit:
      * 0 forward sgemm, 1 backward dot/axpy products, 2 naive tt_matmul. */
     int rule;
+    /* Fused elementwise steps of the epilogue, applied to the finished product (bias included)
+     * BEFORE it is stored or added into C:
+     *   relu  v = v > 0 ? v : 0                      (tt_relu, src/ops.c:104-106)
+     *   mask  v = mask[m * ldmask + n] > 0 ? v : 0   (backward_relu, src/autograd.c:318-327, with
+     *         the relu's OUTPUT as the mask: y > 0 exactly when x > 0, NaN included) */
+    int relu;
+    const float *mask; long ldmask;
 } GemmArgs;
 
 int tt_gemm(const GemmArgs *g);                 /* dispatch by g_tt.gemm_path */
@@ -144,5 +168,7 @@ int tt_peer_usable(const float *p, size_t count);
 int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream);
 int tt_peer_poll_status(void);
 void tt_peer_finalize(void);
+/* dist.cu: per-collective timing while tracing is on */
+void tt_dist_trace_reset(void);
 
 #endif

@@ -71,6 +71,43 @@ def connect(ns, rank, world, peer_floats=0):
         ns.status(ns.LIB.ttb_dist_peer_import(rank, world, blob), "ttb_dist_peer_import")
 
 
+def finalize(ns):
+    """End the job's communication on every rank, in the order CUDA requires for memory that
+    was exported to other processes: everybody stops using the peer blocks (barrier), everybody
+    closes the blocks it imported, a second barrier, and only then does each rank free its own
+    block and destroy the communicator.  No rank returns from here before all have freed."""
+    barrier()
+    ns.LIB.ttb_dist_peer_close()
+    barrier()
+    ns.LIB.ttb_dist_finalize()
+    barrier()
+
+
+def all_sum(values):
+    """Element-wise sum of a list of Python floats over all ranks (float64)."""
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        return list(values)
+    import torch
+    t = torch.tensor(list(values), dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return [float(v) for v in t.tolist()]
+
+
+def max_abs_diff_from_rank0(arr):
+    """max |arr - rank 0's arr| over all elements and ranks (0.0 when the replicas are identical)."""
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        return 0.0
+    import torch
+    mine = torch.from_numpy(arr.reshape(-1).copy())
+    ref = mine.clone()
+    dist.broadcast(ref, src=0)
+    d = (mine.double() - ref.double()).abs().max().reshape(1)
+    dist.all_reduce(d, op=dist.ReduceOp.MAX)
+    return float(d.item())
+
+
 def all_max(value):
     """Max of a Python float over all ranks (1-rank: the value itself)."""
     import torch.distributed as dist

@@ -254,6 +254,27 @@ class MLPTrainer:
             n.release()
         return loss
 
+    def evaluate(self, x_t, y_t):
+        """How many rows of the batch the model classifies as their label: the forward graph of
+        step() in forward-only mode (no graph recorded, every activation freed as soon as the next
+        layer has consumed it, relu inside the GEMM epilogues) and the arg-max / hit count on the
+        device -- evaluate() of tests/gate_mnist_mlp.py:74-80 without the logits leaving the GPU."""
+        ns = self.ns
+        with ns.no_grad():
+            h = ns.Node.from_tensor(x_t, False)
+            for i, w in enumerate(self.params):
+                p = h.padones()
+                z = p.matmul(w)
+                h.release(); p.release()
+                if i + 1 < len(self.params):
+                    h = z.relu()
+                    z.release()
+                else:
+                    h = z
+            correct = ns.argmax_correct(h.value_tensor(), y_t)
+            h.release()
+        return correct
+
     def weights(self):
         return [w.value() for w in self.params]
 
