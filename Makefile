@@ -6,16 +6,18 @@
 NVCC    ?= /usr/local/cuda/bin/nvcc
 HOSTCXX ?= /usr/bin/g++
 ARCH    := -gencode arch=compute_100a,code=sm_100a
-NVFLAGS := $(ARCH) -O3 -std=c++17 -lineinfo -Xcompiler -fPIC -ccbin $(HOSTCXX) -Iinclude -Itinytorch_b200/csrc
+# EXTRA=-DTT_TUNING builds the library with its timing aids and TT_TC_* environment knobs (never for production)
+EXTRA   ?=
+NVFLAGS := $(ARCH) -O3 -std=c++17 -lineinfo -Xcompiler -fPIC -ccbin $(HOSTCXX) -Iinclude -Itinytorch_b200/csrc $(EXTRA)
 SRC     := tinytorch_b200/csrc
 BUILD   := build
 OBJDIR  := $(BUILD)/obj
 # -fmad=false: the exact-fp32 and elementwise kernels round every multiply and
 # add separately, like the reference's C; only explicit fmaf() fuses.
 EXACT   := context tensor ops autograd dist peer_reduce kernels_elementwise kernels_spatial kernels_pipeline gemm_simt
-FAST    := gemm_tc
+FAST    := gemm_tc conv_tc
 OBJS    := $(addprefix $(OBJDIR)/,$(addsuffix .o,$(EXACT) $(FAST)))
-HDRS    := $(wildcard include/*.h) $(SRC)/tt_internal.h
+HDRS    := $(wildcard include/*.h) $(SRC)/tt_internal.h $(SRC)/tcgen05_utils.cuh
 
 PYBIND_INC := $(shell python3 -m pybind11 --includes 2>/dev/null)
 EXT_SUFFIX := $(shell python3-config --extension-suffix 2>/dev/null || echo ".so")
@@ -29,7 +31,7 @@ $(OBJDIR):
 $(addprefix $(OBJDIR)/,$(addsuffix .o,$(EXACT))): $(OBJDIR)/%.o: $(SRC)/%.cu $(HDRS) | $(OBJDIR)
 	$(NVCC) $(NVFLAGS) -fmad=false -c $< -o $@
 
-$(OBJDIR)/gemm_tc.o: $(SRC)/gemm_tc.cu $(HDRS) | $(OBJDIR)
+$(addprefix $(OBJDIR)/,$(addsuffix .o,$(FAST))): $(OBJDIR)/%.o: $(SRC)/%.cu $(HDRS) | $(OBJDIR)
 	$(NVCC) $(NVFLAGS) -c $< -o $@
 
 tinytorch_b200/libtinytorch.so: $(OBJS)

@@ -643,8 +643,19 @@ def run_cnn(args):
         tr.step(xt, yt).release()
     ns.LIB.ttb_event_record(e1)
     ms = ns.LIB.ttb_event_elapsed_ms(e0, e1) / reps
+    launches_per_step = int(ns.LIB.ttb_launch_count() - l1) // reps
+    # where the GPU time of a step goes (a second, traced pass: the event pairs cost host time)
+    ns.LIB.ttb_trace_reset(); ns.LIB.ttb_trace_enable(1)
+    for _ in range(reps):
+        tr.step(xt, yt).release()
+    classes = {}
+    for kind, name in enumerate(["gemm_tcgen05", "gemm_exact_fp32", "elementwise", "softmax", "spatial", "reduce", "optimizer"]):
+        cms, n, _ = ns.trace_read(kind)
+        if n:
+            classes[name] = {"ms_per_step": cms / reps, "launches_per_step": n / reps}
+    ns.LIB.ttb_trace_enable(0)
     line["device_resident"] = {"value": 256 / (ms * 1e-3), "unit": "samples/s", "ms_per_step": ms,
-                               "launches_per_step": int(ns.LIB.ttb_launch_count() - l1) // reps,
+                               "launches_per_step": launches_per_step, "kernel_classes": classes,
                                "what": "parameters stay on the device, fused softmax-cross-entropy seed, SGD kernels; CUDA events"}
     tr.close(); xt.release(); yt.release()
     if not args.no_cpu_baseline:

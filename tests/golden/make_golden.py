@@ -3,7 +3,7 @@
 
 Run in a container that has the reference sources:
 
-    make -C oracle            # builds oracle/_ref/libtinytorch_ref.so from the reference checkout (REF=...)
+    make -C oracle REF=<reference checkout>   # builds oracle/_ref/libtinytorch_ref.so from its sources
     python tests/golden/make_golden.py
 
 Every array written here is an output of the reference's own C code
@@ -194,7 +194,7 @@ def steps_fixture(ref):
 def main():
     ref = O.load_ref()
     if ref is None:
-        sys.exit("oracle/_ref/libtinytorch_ref.so is missing: run `make -C oracle` where the reference sources exist")
+        sys.exit("oracle/_ref/libtinytorch_ref.so is missing: run `make -C oracle REF=<reference checkout>`")
     np.savez_compressed(os.path.join(HERE, "ops.npz"), **ops_fixture(ref))
     np.savez_compressed(os.path.join(HERE, "steps.npz"), **steps_fixture(ref))
     for f in ("ops.npz", "steps.npz"):

@@ -52,7 +52,7 @@ struct AGNode {
     int     is_param;      /* gradient is all-reduced across ranks when final */
     int     fused_pad;     /* matmul that consumed its padones parent virtually */
     float   sgd_lr;        /* > 0: value -= sgd_lr * grad as soon as the gradient is final */
-    int     reduced_in_rule;   /* the rule that produced the gradient already reduced/applied it in chunks */
+    int     reduced_in_rule;   /* the rule that produced the gradient already: 1 reduced and applied it (in chunks), 2 started its reduction */
     int     grad_is_seed;      /* grad is the caller's seed tensor, shared: replace, never write */
 };
 
@@ -259,24 +259,34 @@ static float *grad_target(AGNode *p, int *accumulate) {
     return TT(t)->dev;
 }
 
-/* Elements [off, off+count) of a parameter's gradient are final: sum them over the ranks
- * (marked parameters, communicator present) and, for a parameter with a fused optimiser,
- * apply w -= lr * g right behind the reduction on the same stream.  With a communicator
- * both run on the communication stream, under the backward kernels still to come;
- * ttb_dist_join orders the compute stream after them. */
+/* Elements [off, off+count) of a parameter's gradient are final.  Two steps, which may be issued
+ * together or apart:
+ *   reduce  sum them over the ranks (marked parameters, communicator present) on the communication
+ *           stream, ordered after the kernel that produced them;
+ *   update  for a parameter with a fused optimiser, w -= lr * g behind the reduction on the same
+ *           stream.  The update overwrites the WEIGHTS, which the input-gradient product of the same
+ *           layer still reads: it is ordered after everything enqueued on the compute stream so far,
+ *           so it has to be issued once that product has been enqueued.
+ * With a communicator both run on the communication stream, under the backward kernels still to
+ * come; ttb_dist_join orders the compute stream after them. */
 void tt_dist_note_comm_work(void);
-static void param_grad_ready(AGNode *p, long off, long count) {
+int tt_dist_comm_after_compute(void);
+enum { PARAM_REDUCE = 1, PARAM_UPDATE = 2 };
+static void param_grad_ready(AGNode *p, long off, long count, int steps) {
     if (!p->grad || count <= 0) return;
     const int dist = tt_dist_active() && p->is_param;
     if (!dist && p->sgd_lr <= 0.0f) return;
     float *g = tt_dev_rw(p->grad);
     if (!g) return;
-    if (dist) tt_dist_allreduce_range(g + off, (size_t)count);
-    if (p->sgd_lr > 0.0f) {
+    if (dist && (steps & PARAM_REDUCE)) tt_dist_allreduce_range(g + off, (size_t)count);
+    if (p->sgd_lr > 0.0f && (steps & PARAM_UPDATE)) {
         float *w = tt_dev_rw(p->val);
         if (!w) return;
         cudaStream_t keep = g_tt.stream;
-        if (dist) g_tt.stream = g_tt.comm_stream;
+        if (dist) {
+            if (!(steps & PARAM_REDUCE)) tt_dist_comm_after_compute();      /* the reduction was issued earlier: order after the readers of w */
+            g_tt.stream = g_tt.comm_stream;
+        }
         k_sgd(w + off, g + off, p->sgd_lr, count);
         g_tt.stream = keep;
         if (dist) tt_dist_note_comm_work();
@@ -285,7 +295,7 @@ static void param_grad_ready(AGNode *p, long off, long count) {
         /* the communication stream is still working on both payloads: a release before
          * ttb_dist_join (ag_zero_grad, ag_release) must not recycle their blocks under it */
         tt_mark_busy(p->grad, g_tt.comm_stream);
-        if (p->sgd_lr > 0.0f) tt_mark_busy(p->val, g_tt.comm_stream);
+        if (p->sgd_lr > 0.0f && (steps & PARAM_UPDATE)) tt_mark_busy(p->val, g_tt.comm_stream);
     }
 }
 
@@ -307,26 +317,8 @@ static void bw_matmul(AGNode *n) {
     if (n->fused_pad) {
         AGNode *x = a->parents[0];
         const int Kr = (int)x->val->shape[1];
-        if (x->requires_grad) {               /* dX = dC * W[:K]^T, bypassing the padones node */
-            const float *pw = tt_dev_ro(b->val);
-            /* x is a relu node and this product is all of its gradient: mask it here (the relu's
-             * output is the mask) and hand it to the relu's parent; the relu node's own rule then
-             * finds no gradient and does nothing (src/autograd.c:318-327 folded into :308-316) */
-            AGNode *z = (g_tt.fuse_relu && x->kind == OP_RELU && !x->grad && x->pending == 1 && a->pending == 1 &&
-                         x->nparents == 1 && x->parents[0]->requires_grad) ? x->parents[0] : nullptr;
-            const float *pm = z ? tt_dev_ro(x->val) : nullptr;
-            if (z && !pm) z = nullptr;
-            int acc;
-            float *dst = pw ? grad_target(z ? z : x, &acc) : nullptr;
-            if (dst) {
-                memset(&g, 0, sizeof g);
-                g.tb = 1; g.M = M; g.N = Kr; g.K = N;
-                g.A = pg; g.lda = N; g.B = pw; g.ldb = N; g.C = dst; g.ldc = Kr;
-                g.accumulate = acc; g.rule = 1;
-                if (z) { g.mask = pm; g.ldmask = Kr; }
-                tt_gemm(&g);
-            }
-        }
+        /* the weight gradient first: its all-reduce (data parallel) then starts one product earlier and
+         * runs under the input-gradient product; the two are independent */
         if (b->requires_grad) {               /* dW = [X 1]^T * dC */
             const float *px = tt_dev_ro(x->val);
             int acc;
@@ -350,7 +342,7 @@ static void bw_matmul(AGNode *n) {
                     g.A = px + r0; g.lda = Kr; g.B = pg; g.ldb = N; g.C = dst + (long)r0 * N; g.ldc = N;
                     g.accumulate = acc; g.rule = 1;
                     if (tt_gemm(&g) != 0) break;
-                    param_grad_ready(b, (long)r0 * N, (long)(r1 - r0 + last) * N);
+                    param_grad_ready(b, (long)r0 * N, (long)(r1 - r0 + last) * N, PARAM_REDUCE | PARAM_UPDATE);
                 }
                 b->reduced_in_rule = 1;
             } else if (dst) {
@@ -358,6 +350,32 @@ static void bw_matmul(AGNode *n) {
                 g.ta = 1; g.a_pad_ones = 1; g.M = Kr + 1; g.N = N; g.K = M;
                 g.A = px; g.lda = Kr; g.B = pg; g.ldb = N; g.C = dst; g.ldc = N;
                 g.accumulate = acc; g.rule = 1;
+                if (tt_gemm(&g) == 0 && b->pending == 1 && (b->is_param || b->sgd_lr > 0.0f)) {
+                    /* this was the parameter's last consumer: start its reduction now, under the
+                     * input-gradient product below; the update follows once that product (which reads
+                     * the weights) has been enqueued */
+                    param_grad_ready(b, 0, b->grad->numel, PARAM_REDUCE);
+                    b->reduced_in_rule = 2;
+                }
+            }
+        }
+        if (x->requires_grad) {               /* dX = dC * W[:K]^T, bypassing the padones node */
+            const float *pw = tt_dev_ro(b->val);
+            /* x is a relu node and this product is all of its gradient: mask it here (the relu's
+             * output is the mask) and hand it to the relu's parent; the relu node's own rule then
+             * finds no gradient and does nothing (src/autograd.c:318-327 folded into :308-316) */
+            AGNode *z = (g_tt.fuse_relu && x->kind == OP_RELU && !x->grad && x->pending == 1 && a->pending == 1 &&
+                         x->nparents == 1 && x->parents[0]->requires_grad) ? x->parents[0] : nullptr;
+            const float *pm = z ? tt_dev_ro(x->val) : nullptr;
+            if (z && !pm) z = nullptr;
+            int acc;
+            float *dst = pw ? grad_target(z ? z : x, &acc) : nullptr;
+            if (dst) {
+                memset(&g, 0, sizeof g);
+                g.tb = 1; g.M = M; g.N = Kr; g.K = N;
+                g.A = pg; g.lda = N; g.B = pw; g.ldb = N; g.C = dst; g.ldc = Kr;
+                g.accumulate = acc; g.rule = 1;
+                if (z) { g.mask = pm; g.ldmask = Kr; }
                 tt_gemm(&g);
             }
         }
@@ -449,12 +467,31 @@ static void bw_conv2d(AGNode *n) {
     }
     if (!w->requires_grad && !a->requires_grad) return;
 
+    /* implicit GEMMs where the forward pass would have used one: dW and dX straight from the image
+     * and the output gradient, no col, d_col or permuted copy of g */
+    const ConvGeom cg = {N, C, H, W, F, HH, WW, sh, sw, ph, pw, Ho, Wo};
+    const bool implicit = g_tt.conv_implicit && g_tt.gemm_path != 2 && (double)ncol * F * kc >= (double)(1l << 21);
+    bool dw_done = !w->requires_grad, dx_done = !a->requires_grad;
+    if (implicit && !dw_done && conv_tc_usable(&cg, 0)) {
+        const float *px = tt_dev_ro(a->val);
+        int acc;
+        float *dst = px ? grad_target(w, &acc) : nullptr;
+        if (dst) { conv_tc_wgrad(&cg, px, pg, dst, acc); dw_done = true; }      /* a failed launch is reported, not retried another way */
+    }
+    if (implicit && !dx_done && conv_tc_usable(&cg, 1)) {
+        const float *pwt = tt_dev_ro(w->val);
+        int acc;
+        float *dst = pwt ? grad_target(a, &acc) : nullptr;
+        if (dst) { conv_tc_dgrad(&cg, pg, pwt, dst, acc); dx_done = true; }
+    }
+    if (dw_done && dx_done) return;
+
     float *gp = (float *)tt_dev_alloc(sizeof(float) * (size_t)F * ncol);
     if (!gp) return;
     k_conv_permute(pg, N, F, sp, gp);
     GemmArgs m;
 
-    if (w->requires_grad) {
+    if (!dw_done) {
         const float *px = tt_dev_ro(a->val);
         float *col = px ? (float *)tt_dev_alloc(sizeof(float) * (size_t)kc * ncol) : nullptr;
         Tensor *gw = col ? tt_new_like(w->val, 0) : nullptr;
@@ -468,7 +505,7 @@ static void bw_conv2d(AGNode *n) {
         }
         tt_dev_free(col);
     }
-    if (a->requires_grad) {
+    if (!dx_done) {
         const float *pwt = tt_dev_ro(w->val);
         float *dcol = pwt ? (float *)tt_dev_alloc(sizeof(float) * (size_t)kc * ncol) : nullptr;
         Tensor *ga = dcol ? tt_new_like(a->val, 0) : nullptr;
@@ -609,8 +646,8 @@ static void run_backward(AGNode *out, const float *seed_host, const Tensor *seed
                 if (n->grad && n->nparents > 0) backward_rule(n);
                 for (int k = 0; k < n->nparents; k++) {
                     AGNode *p = n->parents[k];
-                    if (--p->pending == 0 && p->grad && !p->reduced_in_rule && (p->is_param || p->sgd_lr > 0.0f))
-                        param_grad_ready(p, 0, p->grad->numel);
+                    if (--p->pending == 0 && p->grad && p->reduced_in_rule != 1 && (p->is_param || p->sgd_lr > 0.0f))
+                        param_grad_ready(p, 0, p->grad->numel, p->reduced_in_rule == 2 ? PARAM_UPDATE : PARAM_REDUCE | PARAM_UPDATE);
                 }
             }
         }

@@ -12,7 +12,7 @@
 #include <unordered_map>
 #include <vector>
 
-TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, -1, 1, 0, 0};    /* -1: take the setting from the environment */
+TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, -1, -1, 1, 0, 0};    /* -1: take the setting from the environment */
 
 static char g_err[512] = "";
 
@@ -79,6 +79,7 @@ static int ctx_open(int device) {
     if (g_tt.gemm_path < 0) g_tt.gemm_path = env_int("TT_GEMM_PATH", 0);
     if (g_tt.fuse_padones < 0) g_tt.fuse_padones = env_int("TT_FUSE_PADONES", 1);
     if (g_tt.fuse_relu < 0) g_tt.fuse_relu = env_int("TT_FUSE_RELU", 1);
+    if (g_tt.conv_implicit < 0) g_tt.conv_implicit = env_int("TT_CONV_IMPLICIT", 1);
     g_tt.ready = 1;
     return 0;
 }

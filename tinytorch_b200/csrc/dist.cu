@@ -166,6 +166,14 @@ static int reduce_on_comm_stream(float *p, size_t count) {
     return rc;
 }
 
+/* Order the communication stream after everything enqueued on the compute stream so far. */
+int tt_dist_comm_after_compute(void) {
+    if (!tt_dist_active()) return 0;
+    if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
+        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
+    return 0;
+}
+
 int tt_dist_allreduce_async(Tensor *t) {
     if (!tt_dist_active()) return 0;
     float *p = tt_dev_rw(t);

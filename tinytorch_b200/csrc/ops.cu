@@ -319,6 +319,15 @@ extern "C" Tensor *tt_conv2d(const Tensor *a, const Tensor *w, const Tensor *b,
     if (!px || !pw_ || (b && !pb)) return nullptr;
     long shp[4] = {N, F, Ho, Wo};
     Tensor *out = tt_new_uninit(shp, 4);
+    /* implicit GEMM: the image is read through the index map, no col matrix, no permute pass.  Small
+     * problems and the exact-fp32 setting keep the literal im2col + sgemm route below (bit-identical
+     * to the reference). */
+    const ConvGeom cg = {N, C, H, W, F, HH, WW, stride_h, stride_w, pad_h, pad_w, Ho, Wo};
+    if (out && g_tt.conv_implicit && g_tt.gemm_path != 2 && (double)ncol * F * kc >= (double)(1l << 21) &&
+        conv_tc_usable(&cg, 0)) {
+        if (conv_tc_fprop(&cg, px, pw_, pb, TT(out)->dev) != 0) { tt_release(out); return nullptr; }
+        return out;
+    }
     float *col = (float *)tt_dev_alloc(sizeof(float) * (size_t)kc * ncol);
     float *om = (float *)tt_dev_alloc(sizeof(float) * (size_t)F * ncol);
     if (!out || !col || !om) { tt_release(out); tt_dev_free(col); tt_dev_free(om); return nullptr; }

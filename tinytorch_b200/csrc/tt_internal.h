@@ -48,6 +48,7 @@ typedef struct TTContext {
     int          gemm_path;    /* 0 auto, 1 tensor core, 2 exact fp32 */
     int          fuse_padones; /* fold padones into the adjoining GEMM */
     int          fuse_relu;    /* fold relu and its gradient mask into the adjoining GEMMs' epilogues */
+    int          conv_implicit; /* convolutions as implicit GEMMs (no im2col matrix) where the shape allows */
     int          grad_enabled; /* 0: builders record no graph (forward-only / evaluation batches) */
     int          trace;
     long         launches;
@@ -158,6 +159,15 @@ int gemm_simt(const GemmArgs *g);               /* gemm_simt.cu: exact fp32, k a
 int gemm_tc(const GemmArgs *g);                 /* gemm_tc.cu: tcgen05 3xTF32 */
 int gemm_tc_usable(const GemmArgs *g);          /* alignment rules of the TMA path */
 int gemm_tc_poll_status(void);                  /* non-zero (reason stored) when a kernel gave up on a bounded wait */
+
+/* ---- implicit-GEMM convolution (conv_tc.cu) -----------------------------------
+ * x [N,C,H,W], filters [F,C,HH,WW], strides (sh,sw), zero padding (ph,pw), output [N,F,Ho,Wo]. */
+typedef struct ConvGeom { int N, C, H, W, F, HH, WW, sh, sw, ph, pw, Ho, Wo; } ConvGeom;
+int conv_tc_usable(const ConvGeom *g, int need_dgrad);      /* 1 when the gathered tensor-core kernel takes this shape */
+int conv_tc_fprop(const ConvGeom *g, const float *x, const float *w, const float *bias, float *out);
+int conv_tc_dgrad(const ConvGeom *g, const float *grad_out, const float *w, float *dx, int accumulate);
+int conv_tc_wgrad(const ConvGeom *g, const float *x, const float *grad_out, float *dw, int accumulate);
+int conv_tc_poll_status(void);
 
 /* dist.cu: called by the backward pass when a marked leaf's gradient is final. */
 int tt_dist_active(void);
