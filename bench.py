@@ -267,14 +267,16 @@ TENSOR_PIPE_NCU = {"value": 0.70, "case": "4096^3, gemm_tc2_kernel", "source": "
 
 
 def weights_checksum(ws, samples_per_param=25):
-    """float64 sums of every parameter plus a few fixed entries: equal (to rounding of the different
-    reduction orders) for every number of GPUs after the same number of steps."""
+    """float64 checksums of every parameter plus a few fixed entries: equal (to rounding of the
+    different reduction orders) for every number of GPUs after the same number of steps.  The norms
+    are the figures to compare across N; a plain sum of zero-mean weights is 5e-4 of their absolute
+    sum, so it magnifies the same differences two thousand times and is not reported."""
     rng = np.random.default_rng(12345)
-    out = {"sum": [], "abs_sum": [], "samples": [], "replicas_max_abs_diff": 0.0}
+    out = {"abs_sum": [], "l2": [], "samples": [], "replicas_max_abs_diff": 0.0}
     for w in ws:
         w64 = w.astype(np.float64)
-        out["sum"].append(float(w64.sum()))
         out["abs_sum"].append(float(np.abs(w64).sum()))
+        out["l2"].append(float(np.sqrt((w64 * w64).sum())))
         idx = rng.integers(0, w.size, size=samples_per_param)
         out["samples"].extend(float(v) for v in w.reshape(-1)[idx])
         out["replicas_max_abs_diff"] = max(out["replicas_max_abs_diff"], D.max_abs_diff_from_rank0(w))
@@ -343,7 +345,7 @@ def run_ours(args):
     last.release()
     # the parameters after warm-up + 2 + timed steps: float64 checksums (comparable across N: the same
     # number of steps has run on the same global batch) and the largest difference between replicas
-    checksum = weights_checksum(trainer.weights())
+    checksum = None if args.no_checksum else weights_checksum(trainer.weights())
     ms_total = D.all_max(float(ms_total))
     ms_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_step * 1e-3)
@@ -689,6 +691,7 @@ def main():
                     help="tuning aid: a smaller global batch reproduces the per-GPU shapes of a larger job on fewer GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
+    ap.add_argument("--no-checksum", action="store_true", help="tuning runs: skip the parameter checksums (218 MB per rank to the host)")
     ap.add_argument("--small", action="store_true",
                     help="kernels workload: a quarter of the rows and images, one warm-up and one timed launch each")
     ap.add_argument("--workload", choices=["mlp", "gemm", "gemm-sweep", "kernels", "cnn"], default="mlp")

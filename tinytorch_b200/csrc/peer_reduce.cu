@@ -93,8 +93,9 @@ __device__ __forceinline__ void pr_signal_and_wait(const PeerParams &p, int phas
                     pr_poison_all(p);
                     break;
                 }
-                if ((n & 63u) == 0u && pr_poisoned(p)) {          /* somebody else gave up: so do we */
-                    *(volatile unsigned *)p.status = 0x200u | ((unsigned)phase << 4) | (unsigned)t;
+                if ((n & 63u) == 0u && pr_poisoned(p)) {          /* somebody else gave up (another rank, or another CTA of this one): so do we */
+                    if (*(volatile unsigned *)p.status == 0u)      /* the first report stands: it names the wait that ran out */
+                        *(volatile unsigned *)p.status = 0x200u | ((unsigned)phase << 4) | (unsigned)t;
                     *(volatile int *)gave_up = 1;
                     break;
                 }
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(PR_THREADS, 3) peer_allreduce_kernel(PeerParam
         gave_up = 0;
         if (pr_poisoned(p)) {            /* a wait ran out earlier, here or on a peer: flags and staging are not to be trusted */
             gave_up = 1;
-            *(volatile unsigned *)p.status = 0x300u | (unsigned)p.rank;
+            if (*(volatile unsigned *)p.status == 0u) *(volatile unsigned *)p.status = 0x300u | (unsigned)p.rank;
         }
     }
     __syncthreads();
