@@ -325,7 +325,23 @@ static void bw_matmul(AGNode *n) {
             float *dst = px ? grad_target(b, &acc) : nullptr;
             static int dp_chunks = -1;
             if (dp_chunks < 0) { const char *e = getenv("TT_DP_CHUNKS"); dp_chunks = e && *e ? atoi(e) : 2; if (dp_chunks < 1) dp_chunks = 1; }
-            if (dst && dp_chunks > 1 && tt_dist_active() && b->is_param && b->pending == 1 && Kr >= 2048 &&
+            /* Data parallel with the peer-memory reduction: the product's epilogue delivers every block of
+             * the gradient that another rank owns straight into that rank's staging area (reduce-scatter
+             * fused into the GEMM); the reduction kernel that follows only has to move the bias row. */
+            PeerPush pp;
+            const bool fuse_push = dst && !acc && tt_dist_active() && b->is_param && b->pending == 1 && (N & 31) == 0 &&
+                                   tt_peer_push_plan(dst, (size_t)b->grad->numel, &pp);
+            if (fuse_push) {
+                memset(&g, 0, sizeof g);
+                g.ta = 1; g.a_pad_ones = 1; g.M = Kr + 1; g.N = N; g.K = M;
+                g.A = px; g.lda = Kr; g.B = pg; g.ldb = N; g.C = dst; g.ldc = N;
+                g.rule = 1; g.push = &pp;
+                if (tt_gemm(&g) == 0) {
+                    tt_dist_allreduce_pushed(dst, (size_t)b->grad->numel, (size_t)g_tt.gemm_pushed_floats);
+                    tt_mark_busy(b->grad, g_tt.comm_stream);
+                    b->reduced_in_rule = 2;               /* the update follows once the dX product has been enqueued */
+                }
+            } else if (dst && dp_chunks > 1 && tt_dist_active() && b->is_param && b->pending == 1 && Kr >= 2048 &&
                 !x->requires_grad) {
                 /* Data parallel, first layer (its input needs no gradient, so this is the last GEMM
                  * of the pass and nothing is left to hide its all-reduce behind): produce the

@@ -12,7 +12,7 @@
 #include <unordered_map>
 #include <vector>
 
-TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, -1, -1, 1, 0, 0};    /* -1: take the setting from the environment */
+TTContext g_tt = {0, 0, 0, 0, nullptr, nullptr, nullptr, -1, -1, -1, -1, 1, 0, 0, 0};    /* -1: take the setting from the environment */
 
 static char g_err[512] = "";
 

@@ -174,6 +174,20 @@ int tt_dist_comm_after_compute(void) {
     return 0;
 }
 
+/* The reduction of a gradient whose producing GEMM already pushed its first pushed_floats values to
+ * their owners (fused reduce-scatter): peer-memory kernel only. */
+int tt_dist_allreduce_pushed(float *p, size_t count, size_t pushed_floats) {
+    if (!tt_dist_active() || !count) return 0;
+    if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
+        !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
+    CommPair *tp = g_tt.trace ? pair_from(g_cpairs, g_ncpairs) : nullptr;
+    if (tp) { tp->bytes = 4.0 * (double)count; cudaEventRecord(tp->a, g_tt.comm_stream); }
+    const int rc = tt_peer_allreduce_pushed(p, count, pushed_floats, g_tt.comm_stream);
+    if (tp) cudaEventRecord(tp->b, g_tt.comm_stream);
+    if (rc == 0) g_inflight++;
+    return rc;
+}
+
 int tt_dist_allreduce_async(Tensor *t) {
     if (!tt_dist_active()) return 0;
     float *p = tt_dev_rw(t);

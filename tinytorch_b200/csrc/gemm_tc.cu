@@ -91,6 +91,8 @@ struct TcParams {
      * for the whole item and join with the last chunk.  chunk_kb >= the item's length: one chunk. */
     int chunk_kb;
     int group_m;             /* tile rows per rasterisation group (tc_tile_coords) */
+    int push_on;             /* send the parts of C other ranks own into their staging areas (PeerPush) */
+    PeerPush push;
     uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
 };
 
@@ -513,7 +515,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
                     }
                     const int gc = n0 + c0;
-                    if (row < p.M && gc < p.N) epi_store32(r, gc, p.N, e);
+                    if (row < p.M && gc < p.N) {
+                        if (p.push_on) {
+                            /* fused reduce-scatter: this 32-float block of the flat gradient belongs to chunk c;
+                             * a foreign chunk's block goes into this rank's slot of its owner's staging area */
+                            const long flat = (long)row * p.ldc + gc;
+                            const int c = (int)(flat / p.push.chunk_floats);
+                            EpiRow ep = e;
+                            if (c != p.push.rank)
+                                ep.crow = p.push.stage[c] + (long)p.push.rank * p.push.slot_floats + (flat - (long)c * p.push.chunk_floats) - gc;
+                            epi_store32(r, gc, p.N, ep);
+                        } else {
+                            epi_store32(r, gc, p.N, e);
+                        }
+                    }
                 }
                 if (finish_after && row < p.M) {
                     #pragma unroll 1
@@ -876,7 +891,20 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (lane == 0) mbar_arrive_cluster(lead_tempty + 8 * acc);
                     }
                     const int gc = n0 + c0;
-                    if (row < p.M && gc < p.N) epi_store32(r, gc, p.N, e);
+                    if (row < p.M && gc < p.N) {
+                        if (p.push_on) {
+                            /* fused reduce-scatter: this 32-float block of the flat gradient belongs to chunk c;
+                             * a foreign chunk's block goes into this rank's slot of its owner's staging area */
+                            const long flat = (long)row * p.ldc + gc;
+                            const int c = (int)(flat / p.push.chunk_floats);
+                            EpiRow ep = e;
+                            if (c != p.push.rank)
+                                ep.crow = p.push.stage[c] + (long)p.push.rank * p.push.slot_floats + (flat - (long)c * p.push.chunk_floats) - gc;
+                            epi_store32(r, gc, p.N, ep);
+                        } else {
+                            epi_store32(r, gc, p.N, e);
+                        }
+                    }
                 }
                 if (finish_after && row < p.M) {
                     #pragma unroll 1
@@ -1135,7 +1163,7 @@ int gemm_tc_usable(const GemmArgs *g) {
 }
 
 /* Split-K plan of the launch being prepared (host side, single caller thread). */
-static struct { int splits, kb_per_split; float *partial; int tail_tiles, tail_splits, tail_kb; float *tail_partial; int units; int chunk_kb; } g_plan = {1, 0, nullptr, 0, 0, 0, nullptr, 0, 1 << 30};
+static struct { int splits, kb_per_split; float *partial; int tail_tiles, tail_splits, tail_kb; float *tail_partial; int units; int chunk_kb; int push_on; } g_plan = {1, 0, nullptr, 0, 0, 0, nullptr, 0, 1 << 30, 0};
 
 template <int A_MN, int B_MN, int BN, int BK, int STAGES, int SPLIT_ACC>
 static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
@@ -1154,6 +1182,8 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
     p.relu = g->relu; p.mask = g->mask; p.ldmask = g->ldmask;
     p.chunk_kb = g_plan.chunk_kb;
     p.group_m = g_tc_group_m;
+    p.push_on = g_plan.push_on;
+    if (g_plan.push_on) p.push = *g->push;
     const EpiFused fused = {g->bias, g->accumulate, g->relu, g->mask, g->ldmask};
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
     p.tail_tiles = g_plan.tail_tiles; p.tail_splits = g_plan.tail_splits; p.tail_kb = g_plan.tail_kb;
@@ -1201,6 +1231,8 @@ static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUten
     p.relu = g->relu; p.mask = g->mask; p.ldmask = g->ldmask;
     p.chunk_kb = g_plan.chunk_kb;
     p.group_m = g_tc_group_m;
+    p.push_on = g_plan.push_on;
+    if (g_plan.push_on) p.push = *g->push;
     const EpiFused fused = {g->bias, g->accumulate, g->relu, g->mask, g->ldmask};
     p.splits = g_plan.splits; p.kb_per_split = g_plan.kb_per_split; p.partial = g_plan.partial;
     p.tail_tiles = g_plan.tail_tiles; p.tail_splits = g_plan.tail_splits; p.tail_kb = g_plan.tail_kb;
@@ -1358,6 +1390,11 @@ int gemm_tc(const GemmArgs *g) {
     if (tc_setup() != 0) return -1;
     TcShapePlan pl;
     tc_plan_shape(g->M, g->N, g->K, g_tt.gemm_sms, tt_dist_active() ? ttb_dist_world() : 1, &pl);
+    /* A product that pushes its output to other ranks is finished by its own epilogue everywhere: no
+     * K slices (their partial tiles would be finished by another kernel), no folding into C. */
+    const bool push = g->push && !g->accumulate && !g->bias && !g->relu && !g->mask && g->ldc == g->N && (g->N & 31) == 0;
+    if (push) { pl.splits = 1; pl.kb_per_split = (g->K + pl.bk - 1) / pl.bk; pl.tail_tiles = 0; pl.tail_splits = 0; pl.tail_kb = 0;
+                pl.split_acc = (long)pl.kb_per_split * pl.bk > g_tc_split_k; }
     const int bn = pl.bn, bk = pl.bk;
     const bool pair = pl.pair != 0;
     CUtensorMap ma, mb;
@@ -1381,7 +1418,9 @@ int gemm_tc(const GemmArgs *g) {
      * the largest) without folding, 6.8e-5 with. */
     const long k_slice = (long)pl.kb_per_split * bk;
     const bool fold = pl.split_acc && !g->accumulate && k_slice >= (g->rule == 1 ? 4l : 2l) * g_tc_chunk_k;
-    g_plan.chunk_kb = fold ? g_tc_chunk_k / bk : (1 << 30);
+    g_plan.chunk_kb = (fold && !push) ? g_tc_chunk_k / bk : (1 << 30);
+    g_plan.push_on = push ? 1 : 0;
+    g_tt.gemm_pushed_floats = push ? (long)g->M * g->N : 0;
     g_plan.splits = pl.splits; g_plan.kb_per_split = pl.kb_per_split; g_plan.partial = nullptr;
     g_plan.tail_tiles = pl.tail_tiles; g_plan.tail_splits = pl.tail_splits; g_plan.tail_kb = pl.tail_kb; g_plan.tail_partial = nullptr;
     if (pl.splits > 1) {
@@ -1401,6 +1440,6 @@ int gemm_tc(const GemmArgs *g) {
     if (g_plan.partial) tt_dev_free(g_plan.partial);
     if (g_plan.tail_partial) tt_dev_free(g_plan.tail_partial);
     g_plan.splits = 1; g_plan.partial = nullptr;
-    g_plan.tail_tiles = 0; g_plan.tail_partial = nullptr; g_plan.units = 0; g_plan.chunk_kb = 1 << 30;
+    g_plan.tail_tiles = 0; g_plan.tail_partial = nullptr; g_plan.units = 0; g_plan.chunk_kb = 1 << 30; g_plan.push_on = 0;
     return rc;
 }

@@ -48,6 +48,7 @@ static const float *repitched(const float *src, long rows, long cols, long *pitc
 }
 
 int tt_gemm(const GemmArgs *g) {
+    g_tt.gemm_pushed_floats = 0;
     if (g->M <= 0 || g->N <= 0 || g->K <= 0) { tt_set_error("gemm: empty shape"); return -1; }
     GemmArgs core = *g;
     if (g->a_pad_ones) {

@@ -55,7 +55,8 @@ struct PeerParams {
     long slot4;                     /* words between staging slots */
     int rank, world;
     unsigned epoch;                 /* launch number, the value the flags take */
-    float *stage[PR_MAX_WORLD];     /* staging area of rank p as mapped in this process */
+    long push_from4;                /* words below this index were pushed to their owners by the producing GEMM's epilogue */
+    float *stage[PR_MAX_WORLD];     /* staging area (the one of this launch) of rank p as mapped in this process */
     float *result[PR_MAX_WORLD];    /* result area of rank p */
     unsigned *flags[PR_MAX_WORLD];  /* flag block of rank p */
     unsigned *status;               /* host-mapped: 0 = fine */
@@ -135,7 +136,8 @@ __global__ void __launch_bounds__(PR_THREADS, 3) peer_allreduce_kernel(PeerParam
         const long base = (long)c * p.chunk4;
         float4 *dst = (float4 *)p.stage[c] + (long)p.rank * p.slot4;
         long hi = p.count4 - base < s1 ? p.count4 - base : s1;          /* the last chunk may be short */
-        long k = s0 + t;
+        long lo = p.push_from4 - base > s0 ? p.push_from4 - base : s0;  /* the GEMM's epilogue delivered what lies below push_from4 */
+        long k = lo + t;
         for (; k + 3 * PR_THREADS < hi; k += 4 * PR_THREADS) {
             const float4 v0 = g4[base + k], v1 = g4[base + k + PR_THREADS];
             const float4 v2 = g4[base + k + 2 * PR_THREADS], v3 = g4[base + k + 3 * PR_THREADS];
@@ -198,6 +200,8 @@ static struct {
     unsigned *status_host, *status_dev;
     unsigned wait_limit;             /* 0 = the default */
     int failed;                      /* sticky: a bounded wait ran out in this job */
+    cudaEvent_t done[2];             /* end of the last launch that used staging area 0 / 1 */
+    int done_valid[2];
 } g_peer;
 
 /* How long a device-side wait on another rank may last before the kernel gives up and the
@@ -211,11 +215,18 @@ extern "C" int ttb_dist_set_wait_limit_ms(int ms) {
 
 static size_t pr_slot_floats(size_t max_floats, int world) {
     size_t c = (max_floats + world - 1) / world;
-    return (c + 3) & ~(size_t)3;
+    return (c + 31) & ~(size_t)31;                  /* chunks are whole 32-float blocks: a GEMM epilogue stores such blocks */
+}
+static long pr_chunk4(size_t count, int world) {
+    const long count4 = (long)(count / 4);
+    const long c = (count4 + world - 1) / world;
+    return (c + 7) & ~7l;
 }
 static size_t pr_total_bytes(size_t max_floats, int world) {
-    size_t padded = pr_slot_floats(max_floats, world) * world;      /* staging: world slots; result: the same length */
-    return PR_FLAG_BYTES + 2 * padded * sizeof(float);
+    /* two staging areas of world slots, used by alternate launches (the epilogue of a weight-gradient GEMM
+     * may be filling one while the previous reduction still reads the other), and a result area */
+    size_t padded = pr_slot_floats(max_floats, world) * world;
+    return PR_FLAG_BYTES + 3 * padded * sizeof(float);
 }
 
 /* Allocate this rank's block for gradients of up to max_floats values in a job of `world`
@@ -285,7 +296,28 @@ int tt_peer_usable(const float *p, size_t count) {
     return g_peer.active && count > 0 && count <= g_peer.max_floats && (count & 3) == 0 && (((uintptr_t)p) & 15u) == 0;
 }
 
-int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream) {
+static float *pr_stage_of(int q, unsigned epoch) {
+    const size_t padded_floats = (size_t)g_peer.slot4 * 4 * g_peer.world;
+    return (float *)(g_peer.base[q] + PR_FLAG_BYTES) + (size_t)(epoch & 1u) * padded_floats;
+}
+
+/* The reduction that follows will be launch number epoch + 1 and use staging area (epoch + 1) & 1.
+ * Tell a GEMM where to push; the compute stream first waits for the launch that used that area
+ * last (two launches ago), so nothing it still reads is overwritten. */
+int tt_peer_push_plan(const float *grad, size_t count, PeerPush *out) {
+    if (!tt_peer_usable(grad, count) || g_peer.failed) return 0;
+    const unsigned next = g_peer.epoch + 1;
+    const int buf = (int)(next & 1u);
+    if (g_peer.done_valid[buf] && cudaStreamWaitEvent(g_tt.stream, g_peer.done[buf], 0) != cudaSuccess) { cudaGetLastError(); return 0; }
+    memset(out, 0, sizeof *out);
+    out->world = g_peer.world; out->rank = g_peer.rank;
+    out->chunk_floats = pr_chunk4(count, g_peer.world) * 4;
+    out->slot_floats = g_peer.slot4 * 4;
+    for (int q = 0; q < g_peer.world; q++) out->stage[q] = pr_stage_of(q, next);
+    return 1;
+}
+
+int tt_peer_allreduce_pushed(float *p, size_t count, size_t pushed_floats, cudaStream_t stream) {
     if (g_peer.failed || tt_peer_poll_status()) {
         tt_set_error("peer all-reduce: a bounded wait ran out earlier in this job; the peer path is shut");
         return -1;
@@ -295,21 +327,27 @@ int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream) {
     const size_t padded_floats = (size_t)g_peer.slot4 * 4 * g_peer.world;
     k.g = p;
     k.count4 = (long)(count / 4);
-    k.chunk4 = (k.count4 + g_peer.world - 1) / g_peer.world;
+    k.chunk4 = pr_chunk4(count, g_peer.world);
     k.slot4 = g_peer.slot4;
     k.rank = g_peer.rank; k.world = g_peer.world;
     k.epoch = ++g_peer.epoch;
+    k.push_from4 = (long)(pushed_floats / 4);
     k.status = g_peer.status_dev;
     k.wait_limit = g_peer.wait_limit ? g_peer.wait_limit : PR_WAIT_LIMIT;
     for (int q = 0; q < g_peer.world; q++) {
         k.flags[q] = (unsigned *)g_peer.base[q];
-        k.stage[q] = (float *)(g_peer.base[q] + PR_FLAG_BYTES);
-        k.result[q] = k.stage[q] + padded_floats;
+        k.stage[q] = pr_stage_of(q, k.epoch);
+        k.result[q] = (float *)(g_peer.base[q] + PR_FLAG_BYTES) + 2 * padded_floats;
     }
     peer_allreduce_kernel<<<g_peer.ctas, PR_THREADS, 0, stream>>>(k);
     g_tt.launches++;
+    const int buf = (int)(k.epoch & 1u);
+    if (!g_peer.done[buf] && cudaEventCreateWithFlags(&g_peer.done[buf], cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); g_peer.done[buf] = nullptr; }
+    if (g_peer.done[buf]) { cudaEventRecord(g_peer.done[buf], stream); g_peer.done_valid[buf] = 1; }
     return tt_cuda_ok(cudaGetLastError(), "peer all-reduce launch") ? 0 : -1;
 }
+
+int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream) { return tt_peer_allreduce_pushed(p, count, 0, stream); }
 
 /* Non-zero when a peer kernel gave up on a wait since the last call. */
 int tt_peer_poll_status(void) {
@@ -354,5 +392,6 @@ void tt_peer_finalize(void) {
     if (g_peer.base[0]) { cudaDeviceSynchronize(); cudaFree(g_peer.base[0]); g_peer.base[0] = nullptr; }
     g_peer.epoch = 0;
     g_peer.failed = 0;
+    for (int b = 0; b < 2; b++) { if (g_peer.done[b]) cudaEventDestroy(g_peer.done[b]); g_peer.done[b] = nullptr; g_peer.done_valid[b] = 0; }
     if (g_peer.status_host) *g_peer.status_host = 0;
 }

@@ -52,6 +52,7 @@ typedef struct TTContext {
     int          grad_enabled; /* 0: builders record no graph (forward-only / evaluation batches) */
     int          trace;
     long         launches;
+    long         gemm_pushed_floats;  /* set by tt_gemm: leading floats of C whose foreign chunks went to their owners */
 } TTContext;
 
 extern TTContext g_tt;
@@ -130,6 +131,16 @@ void k_avgpool_bwd(const float *g, long NC, int H, int W, int ph, int pw, int sh
  *   tb == 0: B is [K,N] with row pitch ldb;  tb == 1: B is stored [N,K]
  * accumulate != 0 adds into C.  bias (may be NULL) is one value per column.
  * Returns 0, or -1 with the reason stored. */
+/* Where the epilogue of a weight-gradient product sends what other ranks own (peer_reduce.cu): the
+ * gradient, seen as one flat array, is cut into `world` chunks of chunk_floats; the part of chunk c
+ * computed here goes straight into slot `rank` of rank c's staging area (plain peer stores) instead
+ * of local memory, so the reduce-scatter's transfer happens inside the GEMM. */
+typedef struct PeerPush {
+    float *stage[8];         /* staging area of every rank as mapped in this process */
+    int world, rank;
+    long chunk_floats, slot_floats;
+} PeerPush;
+
 typedef struct GemmArgs {
     int ta, tb;
     int M, N, K;
@@ -152,6 +163,10 @@ typedef struct GemmArgs {
      *         the relu's OUTPUT as the mask: y > 0 exactly when x > 0, NaN included) */
     int relu;
     const float *mask; long ldmask;
+    /* Optional: push the parts of C that other ranks own to them (see PeerPush).  Honoured by the
+     * tensor-core kernel for a plain product into a contiguous C (ldc == N, N a multiple of 32);
+     * g_tt.gemm_pushed_floats tells the caller how many leading floats of C were handled that way. */
+    const PeerPush *push;
 } GemmArgs;
 
 int tt_gemm(const GemmArgs *g);                 /* dispatch by g_tt.gemm_path */
@@ -178,6 +193,11 @@ int tt_peer_usable(const float *p, size_t count);
 int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream);
 int tt_peer_poll_status(void);
 void tt_peer_finalize(void);
+/* Fused reduce-scatter: plan the push of the next reduction (1 when the gradient qualifies), and run
+ * that reduction for a gradient whose first pushed_floats values were pushed by the GEMM. */
+int tt_peer_push_plan(const float *grad, size_t count, PeerPush *out);
+int tt_peer_allreduce_pushed(float *p, size_t count, size_t pushed_floats, cudaStream_t stream);
+int tt_dist_allreduce_pushed(float *p, size_t count, size_t pushed_floats);
 /* dist.cu: per-collective timing while tracing is on */
 void tt_dist_trace_reset(void);
 
