@@ -260,8 +260,8 @@ def gemm_block(ns, peaks, cases=((1024, 5), (4096, 5))):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per tcgen05 GEMM launch, averaged over the launches of
 # one step of this workload at N GPUs (ncu, one step captured; see the named summary).  None: not captured.
-MLP_GEMM_TRAFFIC = {}
-MLP_GEMM_TRAFFIC_SOURCE = None
+MLP_GEMM_TRAFFIC = {1: 648.1e6}
+MLP_GEMM_TRAFFIC_SOURCE = "profiles/mlp_step_gemm_dram_traffic.md (ncu, the 11 GEMM launches of one step; 331 MB algorithmic per launch)"
 # sm__pipe_tensor_cycles_active of the pair kernel, from the ncu capture named here (not an estimate)
 TENSOR_PIPE_NCU = {"value": 0.70, "case": "4096^3, gemm_tc2_kernel", "source": "profiles/gemm_tc2_kernel_square4096.md"}
 

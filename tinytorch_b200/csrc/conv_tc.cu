@@ -64,6 +64,34 @@ struct ConvParams {
     uint32_t *status;
 };
 
+/* Bounded wait for the warps that have nothing else to do (MMA issuer, epilogue): between polls the
+ * thread sleeps, so that the instruction issue slots go to the producer warps, whose index arithmetic
+ * is what bounds this kernel. */
+__device__ __forceinline__ bool cv_wait_idle(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                             uint32_t *status, uint32_t code) {
+    if (mbar_try(bar, parity)) return true;
+    long long t0 = clock64();
+    for (;;) {
+        __nanosleep(100);
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TC_WAIT_CYCLES) {
+            *abort_flag = 1;
+            *(volatile uint32_t *)status = code | (blockIdx.x << 8);
+            __threadfence_system();
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool cv_wait_idle_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                  uint32_t *status, uint32_t code) {
+    bool got = true;
+    if ((threadIdx.x & 31) == 0) got = cv_wait_idle(bar, parity, abort_flag, status, code);
+    got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+    if (got) got = mbar_wait(bar, parity, abort_flag, status, code);     /* immediate: the phase is complete */
+    return __all_sync(0xffffffffu, got);
+}
+
 __device__ __forceinline__ uint32_t cv_swz(uint32_t off) { return off ^ (((off >> 7) & 7u) << 4); }
 
 /* Gather arithmetic.  Every element of an operand tile is src[rowbase + tapoff] or zero:
@@ -210,7 +238,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                 const int s = (int)(seq % p.stages);
                 if (s != grp) continue;
                 const uint32_t ph = (uint32_t)((seq / p.stages) & 1);
-                if (!mbar_wait_warp(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 0x13)) { ok = false; break; }
+                if (!cv_wait_idle_warp(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 0x13)) { ok = false; break; }
                 uint8_t *a_hi = smem_gen + (size_t)s * stage_bytes;
                 uint8_t *b_hi = a_hi + 2 * CV_A_BYTES;
                 const int k0 = kb * CV_BK;
@@ -329,11 +357,11 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
             for (int it = blockIdx.x; it < p.items && ok; it += gridDim.x) {
                 long m0; int kb0, kb1, slice;
                 decode(it, m0, kb0, kb1, slice);
-                if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 0x14)) { ok = false; break; }
+                if (!cv_wait_idle(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 0x14)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(acc * bn32);
                 for (int kb = kb0; kb < kb1; kb++) {
-                    if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 0x12)) { ok = false; break; }
+                    if (!cv_wait_idle(bar_full + 8 * s, ph, abort_flag, p.status, 0x12)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_hi = smem_base + (uint32_t)s * stage_bytes;
                     const uint32_t a_lo = a_hi + CV_A_BYTES;
@@ -378,7 +406,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                     col_stride = spp;
                 }
             }
-            if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 0x15)) { ok = false; break; }
+            if (!cv_wait_idle_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 0x15)) { ok = false; break; }
             tc_fence_after();
             #pragma unroll 1
             for (int c0 = 0; c0 < p.bn; c0 += 32) {
