@@ -164,7 +164,7 @@ def run_reference(args):
     # Every step is the FULL global batch unless the first one predicts that warm-up + timed steps
     # would not fit the budget; only then is a slice of the batch timed and the line says so.
     step(64)                                             # page in, build the thread pool
-    batch, extrapolated = GLOBAL_BATCH, False
+    batch, extrapolated, ran_full_probe = GLOBAL_BATCH, False, False
     n_steps = max(args.warmup, 1) + max(args.steps, 1)
     if args.ref_batch:
         batch, extrapolated = args.ref_batch, args.ref_batch != GLOBAL_BATCH
@@ -172,6 +172,7 @@ def run_reference(args):
         per_sample = step(256) / 256                     # probe: over-estimates the full step (fixed costs spread over fewer samples)
         if per_sample * GLOBAL_BATCH * n_steps > args.ref_budget_s:
             first = step(GLOBAL_BATCH) if kind == "reference" and per_sample * GLOBAL_BATCH < args.ref_budget_s / 4 else None
+            ran_full_probe = first is not None
             if first is not None and first * n_steps <= args.ref_budget_s:
                 pass
             else:
@@ -180,7 +181,7 @@ def run_reference(args):
                 fit = args.ref_budget_s / (n_steps * per_sample)
                 batch = min(GLOBAL_BATCH, max(64, 1 << int(np.floor(np.log2(max(fit, 64))))))
                 extrapolated = batch != GLOBAL_BATCH
-    for _ in range(max(args.warmup, 1)):
+    for _ in range(max(args.warmup, 1) - (1 if ran_full_probe and not extrapolated else 0)):   # the full-batch probe was a warm-up step
         step(batch)
     times = [step(batch) for _ in range(max(args.steps, 1))]
     sec = statistics.median(times)

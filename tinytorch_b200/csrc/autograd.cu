@@ -272,13 +272,17 @@ static float *grad_target(AGNode *p, int *accumulate) {
 void tt_dist_note_comm_work(void);
 int tt_dist_comm_after_compute(void);
 enum { PARAM_REDUCE = 1, PARAM_UPDATE = 2 };
+enum { PARAM_TAIL = 4 };      /* the reduction has nothing left to hide behind: it may use every SM */
 static void param_grad_ready(AGNode *p, long off, long count, int steps) {
     if (!p->grad || count <= 0) return;
     const int dist = tt_dist_active() && p->is_param;
     if (!dist && p->sgd_lr <= 0.0f) return;
     float *g = tt_dev_rw(p->grad);
     if (!g) return;
-    if (dist && (steps & PARAM_REDUCE)) tt_dist_allreduce_range(g + off, (size_t)count);
+    if (dist && (steps & PARAM_REDUCE)) {
+        if (steps & PARAM_TAIL) tt_dist_allreduce_tail(g + off, (size_t)count);
+        else tt_dist_allreduce_range(g + off, (size_t)count);
+    }
     if (p->sgd_lr > 0.0f && (steps & PARAM_UPDATE)) {
         float *w = tt_dev_rw(p->val);
         if (!w) return;
@@ -358,7 +362,7 @@ static void bw_matmul(AGNode *n) {
                     g.A = px + r0; g.lda = Kr; g.B = pg; g.ldb = N; g.C = dst + (long)r0 * N; g.ldc = N;
                     g.accumulate = acc; g.rule = 1;
                     if (tt_gemm(&g) != 0) break;
-                    param_grad_ready(b, (long)r0 * N, (long)(r1 - r0 + last) * N, PARAM_REDUCE | PARAM_UPDATE);
+                    param_grad_ready(b, (long)r0 * N, (long)(r1 - r0 + last) * N, PARAM_REDUCE | PARAM_UPDATE | (last ? PARAM_TAIL : 0));
                 }
                 b->reduced_in_rule = 1;
             } else if (dst) {

@@ -31,7 +31,22 @@ typedef struct { char internal[128]; } ncclUniqueId;
 typedef int ncclResult_t;          /* 0 = ncclSuccess, 7 = ncclInProgress */
 enum { NCCL_FLOAT32 = 7, NCCL_SUM = 0 };
 
+/* ncclConfig_t as of NCCL 2.18 (the first fields of every later version, which accept it by its size and
+ * version fields): what ncclCommInitRankConfig / ncclCommSplit need to cap a communicator's CTAs. */
+typedef struct {
+    size_t size; unsigned int magic; unsigned int version;
+    int blocking; int cgaClusterSize; int minCTAs; int maxCTAs; const char *netName; int splitShare;
+} TtNcclConfig;
+#define TT_NCCL_UNDEF_INT ((int)0x80000000)
+static TtNcclConfig nccl_config(int max_ctas) {
+    TtNcclConfig c = {sizeof(TtNcclConfig), 0xcafebeefu, 21803u, TT_NCCL_UNDEF_INT, TT_NCCL_UNDEF_INT, TT_NCCL_UNDEF_INT,
+                      max_ctas, nullptr, TT_NCCL_UNDEF_INT};
+    return c;
+}
+
 typedef ncclResult_t (*fn_GetUniqueId)(ncclUniqueId *);
+typedef ncclResult_t (*fn_CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, TtNcclConfig *);
+typedef ncclResult_t (*fn_CommSplit)(ncclComm_t, int, int, ncclComm_t *, TtNcclConfig *);
 typedef ncclResult_t (*fn_CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
 typedef ncclResult_t (*fn_AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t);
 typedef ncclResult_t (*fn_CommDestroy)(ncclComm_t);
@@ -48,9 +63,15 @@ static struct {
     fn_CommAbort CommAbort;
     fn_CommGetAsyncError CommGetAsyncError;
     fn_GetErrorString GetErrorString;
+    fn_CommInitRankConfig CommInitRankConfig;      /* optional (NCCL >= 2.14) */
+    fn_CommSplit CommSplit;                        /* optional (NCCL >= 2.18) */
 } nccl;
 
 static ncclComm_t g_comm = nullptr;
+/* A second communicator over the same ranks for the reductions nothing is left to hide behind (the last
+ * row block of the last weight gradient of a pass): the first one is held to the few CTAs that fit beside
+ * the GEMMs, this one may take the SMs the finished backward pass has left idle. */
+static ncclComm_t g_comm_tail = nullptr;
 static int g_world = 1, g_rank = 0;
 static cudaEvent_t g_ev_ready = nullptr, g_ev_done = nullptr;
 static int g_inflight = 0;
@@ -68,6 +89,8 @@ static int nccl_bind(void) {
     nccl.CommAbort = (fn_CommAbort)dlsym(nccl.handle, "ncclCommAbort");
     nccl.CommGetAsyncError = (fn_CommGetAsyncError)dlsym(nccl.handle, "ncclCommGetAsyncError");
     nccl.GetErrorString = (fn_GetErrorString)dlsym(nccl.handle, "ncclGetErrorString");
+    nccl.CommInitRankConfig = (fn_CommInitRankConfig)dlsym(nccl.handle, "ncclCommInitRankConfig");
+    nccl.CommSplit = (fn_CommSplit)dlsym(nccl.handle, "ncclCommSplit");
     if (!nccl.GetUniqueId || !nccl.CommInitRank || !nccl.AllReduce || !nccl.CommDestroy ||
         !nccl.CommAbort || !nccl.CommGetAsyncError || !nccl.GetErrorString) {
         tt_set_error("NCCL library lacks a required symbol");
@@ -102,18 +125,28 @@ extern "C" int ttb_dist_init(int rank, int world, const char id_in[128]) {
     /* From four ranks on the GEMMs leave the SMs their wave count does not need to the collective
      * (gemm_tc.cu, TT_TC_FIT); NCCL is then held to the CTAs that fit there, unless the caller has
      * set NCCL_MAX_CTAS.  Measured together: 8 GPUs 2.65 -> 2.53 ms per step; either one alone loses. */
-    {
-        int fit = 1, from = 4;
+    int fit = 1, from = 4;
 #ifdef TT_TUNING
+    {
         const char *f = getenv("TT_TC_FIT"), *fw = getenv("TT_TC_FIT_WORLD");
         if (f && *f) fit = atoi(f);
         if (fw && *fw) from = atoi(fw);
-#endif
-        if (fit && world >= from) setenv("NCCL_MAX_CTAS", "16", 0);
     }
+#endif
+    const bool cap = fit && world >= from && !getenv("NCCL_MAX_CTAS");
     ncclUniqueId id;
     memcpy(id.internal, id_in, 128);
-    if (!nccl_ok(nccl.CommInitRank(&g_comm, world, id, rank), "ncclCommInitRank")) { g_comm = nullptr; return -1; }
+    if (cap && nccl.CommInitRankConfig && nccl.CommSplit && !getenv("TT_DP_TAIL_COMM_OFF")) {
+        /* main communicator capped by its configuration (not by the environment, which would cap the
+         * second one too); tail communicator split off it with NCCL's own default */
+        TtNcclConfig main_cfg = nccl_config(16);
+        if (!nccl_ok(nccl.CommInitRankConfig(&g_comm, world, id, rank, &main_cfg), "ncclCommInitRankConfig")) { g_comm = nullptr; return -1; }
+        TtNcclConfig tail_cfg = nccl_config(TT_NCCL_UNDEF_INT);
+        if (nccl.CommSplit(g_comm, 0, rank, &g_comm_tail, &tail_cfg) != 0) g_comm_tail = nullptr;     /* optional: the main one serves */
+    } else {
+        if (cap) setenv("NCCL_MAX_CTAS", "16", 0);
+        if (!nccl_ok(nccl.CommInitRank(&g_comm, world, id, rank), "ncclCommInitRank")) { g_comm = nullptr; return -1; }
+    }
     if (!tt_cuda_ok(cudaEventCreateWithFlags(&g_ev_ready, cudaEventDisableTiming), "cudaEventCreate") ||
         !tt_cuda_ok(cudaEventCreateWithFlags(&g_ev_done, cudaEventDisableTiming), "cudaEventCreate")) return -1;
     g_world = world; g_rank = rank;
@@ -152,7 +185,7 @@ static CommPair *pair_from(std::vector<CommPair> &pool, size_t &used) {
 
 /* Sum count floats at p over all ranks in place: ordered after everything already on the
  * compute stream, runs on the communication stream. */
-static int reduce_on_comm_stream(float *p, size_t count) {
+static int reduce_on_comm_stream(float *p, size_t count, int tail = 0) {
     if (!tt_cuda_ok(cudaEventRecord(g_ev_ready, g_tt.stream), "cudaEventRecord") ||
         !tt_cuda_ok(cudaStreamWaitEvent(g_tt.comm_stream, g_ev_ready, 0), "cudaStreamWaitEvent")) return -1;
     CommPair *tp = g_tt.trace ? pair_from(g_cpairs, g_ncpairs) : nullptr;
@@ -160,7 +193,7 @@ static int reduce_on_comm_stream(float *p, size_t count) {
     int rc = 0;
     if (tt_peer_usable(p, count)) {
         if (tt_peer_allreduce(p, count, g_tt.comm_stream) != 0) rc = -1;
-    } else if (!nccl_ok(nccl.AllReduce(p, p, count, NCCL_FLOAT32, NCCL_SUM, g_comm, g_tt.comm_stream), "ncclAllReduce")) rc = -1;
+    } else if (!nccl_ok(nccl.AllReduce(p, p, count, NCCL_FLOAT32, NCCL_SUM, (tail && g_comm_tail) ? g_comm_tail : g_comm, g_tt.comm_stream), "ncclAllReduce")) rc = -1;
     if (tp) cudaEventRecord(tp->b, g_tt.comm_stream);
     if (rc == 0) g_inflight++;
     return rc;
@@ -200,6 +233,11 @@ int tt_dist_allreduce_async(Tensor *t) {
 int tt_dist_allreduce_range(float *p, size_t count) {
     if (!tt_dist_active() || !count) return 0;
     return reduce_on_comm_stream(p, count);
+}
+/* The same for a reduction that no compute is left to overlap with: it may use the tail communicator. */
+int tt_dist_allreduce_tail(float *p, size_t count) {
+    if (!tt_dist_active() || !count) return 0;
+    return reduce_on_comm_stream(p, count, 1);
 }
 
 extern "C" int ttb_dist_allreduce(Tensor *t) {
@@ -249,6 +287,7 @@ extern "C" int ttb_dist_join(void) {
     if (!nccl_ok(nccl.CommGetAsyncError(g_comm, &async), "ncclCommGetAsyncError")) return -1;
     if (async != 0 && async != 7) {
         nccl_ok(async, "NCCL asynchronous error");
+        if (g_comm_tail) { nccl.CommAbort(g_comm_tail); g_comm_tail = nullptr; }
         nccl.CommAbort(g_comm);
         g_comm = nullptr; g_world = 1;
         return -1;
@@ -260,6 +299,7 @@ extern "C" void ttb_dist_finalize(void) {
     tt_peer_finalize();
     if (g_comm) {
         cudaStreamSynchronize(g_tt.comm_stream);
+        if (g_comm_tail) { nccl.CommDestroy(g_comm_tail); g_comm_tail = nullptr; }
         nccl.CommDestroy(g_comm);
         g_comm = nullptr;
     }

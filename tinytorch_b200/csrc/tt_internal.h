@@ -188,6 +188,7 @@ int conv_tc_poll_status(void);
 int tt_dist_active(void);
 int tt_dist_allreduce_async(Tensor *t);
 int tt_dist_allreduce_range(float *p, size_t count);     /* same, for a contiguous part of a gradient */
+int tt_dist_allreduce_tail(float *p, size_t count);      /* same, when nothing is left to overlap it with */
 /* peer-memory all-reduce (peer_reduce.cu) */
 int tt_peer_usable(const float *p, size_t count);
 int tt_peer_allreduce(float *p, size_t count, cudaStream_t stream);
