@@ -83,19 +83,38 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(SimtParams p) {
             fused[i][j] = (MODE == MODE_FWD) && !p.all_edge && gi < p.mfull && gj < p.nfull;
         }
 
-    for (int k0 = 0; k0 < p.K; k0 += BK) {
-        /* stage the tiles; threads run along the contiguous direction of each operand */
+    /* The K loop is a chain of global-load latencies for the small problems this kernel serves (a
+     * 256 x 257 x 10 classifier layer is four blocks of 17 steps): the next step's operands are
+     * fetched into registers while the current step is multiplied out of shared memory.  The order
+     * of the arithmetic is untouched. */
+    float ra[4], rb[4];
+    auto fetch = [&](int k0) {
         #pragma unroll
         for (int r = 0; r < 4; r++) {
-            int e = tid + 256 * r;
-            int kk, mm;
+            const int e = tid + 256 * r;
+            int kk, mm, nn;
             if (p.ta) { mm = e % BM; kk = e / BM; } else { kk = e % BK; mm = e / BK; }
-            As[kk][mm] = load_a(p, m0 + mm, k0 + kk);
-            int nn;
+            ra[r] = load_a(p, m0 + mm, k0 + kk);
             if (p.tb) { kk = e % BK; nn = e / BK; } else { nn = e % BN; kk = e / BN; }
-            Bs[kk][nn] = load_b(p, k0 + kk, n0 + nn);
+            rb[r] = load_b(p, k0 + kk, n0 + nn);
         }
+    };
+    auto stash = [&]() {
+        #pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int e = tid + 256 * r;
+            int kk, mm, nn;
+            if (p.ta) { mm = e % BM; kk = e / BM; } else { kk = e % BK; mm = e / BK; }
+            As[kk][mm] = ra[r];
+            if (p.tb) { kk = e % BK; nn = e / BK; } else { nn = e % BN; kk = e / BN; }
+            Bs[kk][nn] = rb[r];
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < p.K; k0 += BK) {
+        stash();
         __syncthreads();
+        if (k0 + BK < p.K) fetch(k0 + BK);              /* in flight during the multiply below */
         int kmax = p.K - k0 < BK ? p.K - k0 : BK;
         for (int kk = 0; kk < kmax; kk++) {
             float a[4], b[4];
