@@ -174,7 +174,10 @@ int     ttb_grad_enabled(void);
 
 /* ---- autograd extras ------------------------------------------------------
  * ag_backward_from with the seed already on the device: same contract, no
- * host round trip.  Returns 0, or -1 when the element counts differ. */
+ * host round trip.  Returns 0, or -1 when the element counts differ.  When
+ * `out` is an operator node without a gradient yet, the seed tensor is SHARED
+ * as its gradient (retained, not copied): leave its contents alone while the
+ * node lives; a later pass with another seed replaces it. */
 int     ag_backward_from_tensor(AGNode *out, const Tensor *seed);
 /* Drop a node's accumulated gradient so that the next pass starts from zero.
  * Needed once a parameter leaf outlives a step; the reference scripts build

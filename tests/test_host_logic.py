@@ -88,3 +88,52 @@ def test_two_gloo_ranks_reproduce_the_full_batch_gradient(tmp_path):
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert "rank0ok" in out.stdout and "rank1ok" in out.stdout
+
+
+# The host-side plumbing bench.py relies on at N > 1, on two gloo ranks: the global loss from shard
+# means, the replica comparison, and the order of the tear-down calls (observed through a recording
+# stand-in for the library; the calls themselves need a GPU).
+PLUMBING_WORKER = r"""
+import os, sys, time
+import numpy as np
+sys.path.insert(0, sys.argv[1])
+from tinytorch_b200 import dist as D
+rank, world, _ = D.init_process_group("gloo")
+# global mean loss from per-rank shard means, weighted by rows
+rows = [3, 5]
+shard_mean = [2.0, 4.0][rank]
+total = D.all_sum([shard_mean * rows[rank]])[0] / sum(rows)
+assert abs(total - (2.0 * 3 + 4.0 * 5) / 8) < 1e-12
+# replicas: identical arrays give 0, a difference on one rank is found on both
+w = np.arange(12, dtype=np.float32)
+assert D.max_abs_diff_from_rank0(w) == 0.0
+w2 = w.copy()
+if rank == 1:
+    w2[7] += 0.25
+assert D.max_abs_diff_from_rank0(w2) == 0.25
+# tear-down order: nobody frees its block (finalize) before everybody has closed its imports
+log = os.path.join(sys.argv[2], "order.log")
+class Lib:
+    def ttb_dist_peer_close(self):
+        if rank == 1: time.sleep(0.5)            # a slow rank must hold the others back
+        with open(log, "a") as f: f.write("close%d\n" % rank)
+    def ttb_dist_finalize(self):
+        with open(log, "a") as f: f.write("final%d\n" % rank)
+class NS: LIB = Lib()
+D.finalize(NS)
+if rank == 0:
+    seq = open(log).read().split()
+    assert sorted(seq[:2]) == ["close0", "close1"] and sorted(seq[2:]) == ["final0", "final1"], seq
+sys.stdout.write("rank%dok\n" % rank)
+"""
+
+
+def test_two_gloo_ranks_host_plumbing(tmp_path):
+    script = tmp_path / "plumbing.py"
+    script.write_text(PLUMBING_WORKER)
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29613", str(script), ROOT, str(tmp_path)]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "rank0ok" in out.stdout and "rank1ok" in out.stdout
