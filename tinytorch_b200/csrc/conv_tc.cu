@@ -213,6 +213,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
         const uint32_t lo_a = CV_A_BYTES, lo_b = b_bytes;
         const int hw = p.HH * p.WW;
         long seq = 0;                                                   /* running number of the K block in this CTA */
+        int zeroed_for = -1;                                            /* wgrad: item for which this group's stage has its unused rows cleared */
         bool ok = true;
         for (int it = blockIdx.x; it < p.items && ok; it += gridDim.x) {
             long m0; int kb0, kb1, slice;
@@ -304,8 +305,16 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                     }
                     const int valid_rows = (int)(p.rows_a - m0 < CV_BM ? p.rows_a - m0 : CV_BM);
                     const int rstep = gthreads / 8;
+                    /* tile rows beyond the last tap stay zero for the whole item: they are cleared once, the
+                     * first time this group fills its stage for the item (3 -> 32 filters have 27 taps: 101
+                     * of the 128 rows would otherwise be stored, hi and lo, in every K block) */
+                    if (zeroed_for != it) {
+                        for (int r = valid_rows + (gt >> 3); r < CV_BM; r += rstep)
+                            cv_put(a_hi, lo_a, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), make_float4(0.0f, 0.0f, 0.0f, 0.0f));
+                        zeroed_for = it;
+                    }
                     /* eight rows' loads (32 per thread) in flight at a time */
-                    for (int r0 = gt >> 3; r0 < CV_BM; r0 += 8 * rstep) {
+                    for (int r0 = gt >> 3; r0 < valid_rows; r0 += 8 * rstep) {
                         float4 v[8];
                         #pragma unroll
                         for (int j = 0; j < 8; j++) {
@@ -319,7 +328,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                         #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int r = r0 + j * rstep;
-                            if (r < CV_BM) cv_put(a_hi, lo_a, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), v[j]);
+                            if (r < valid_rows) cv_put(a_hi, lo_a, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), v[j]);
                         }
                     }
                     for (int r0 = gt >> 3; r0 < p.bn; r0 += 8 * rstep) {
