@@ -92,6 +92,20 @@ __device__ __forceinline__ bool cv_wait_idle_warp(uint32_t bar, uint32_t parity,
     return __all_sync(0xffffffffu, got);
 }
 
+#ifdef TT_TUNING
+__device__ unsigned long long g_cv_dbg[16];
+extern "C" int ttb_debug_conv_read(unsigned long long out[16]) {
+    cudaStreamSynchronize(g_tt.stream);
+    unsigned long long z[16] = {0};
+    if (cudaMemcpyFromSymbol(out, g_cv_dbg, sizeof z) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(g_cv_dbg, z, sizeof z);
+    return 0;
+}
+#define CV_STAMP(i, t0) do { if (blockIdx.x == 0 && gt == 0 && grp == 0) { long long now_ = clock64(); atomicAdd(&g_cv_dbg[i], (unsigned long long)(now_ - (t0))); (t0) = now_; } } while (0)
+#else
+#define CV_STAMP(i, t0) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t cv_swz(uint32_t off) { return off ^ (((off >> 7) & 7u) << 4); }
 
 /* Gather arithmetic.  Every element of an operand tile is src[rowbase + tapoff] or zero:
@@ -239,33 +253,34 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                 const int s = (int)(seq % p.stages);
                 if (s != grp) continue;
                 const uint32_t ph = (uint32_t)((seq / p.stages) & 1);
-                if (!cv_wait_idle_warp(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 0x13)) { ok = false; break; }
+                long long tstamp = clock64(); (void)tstamp;
                 uint8_t *a_hi = smem_gen + (size_t)s * stage_bytes;
                 uint8_t *b_hi = a_hi + 2 * CV_A_BYTES;
                 const int k0 = kb * CV_BK;
+                /* The stage is still being read by the tensor core while this group comes round again, so
+                 * the loads that fit in registers (the first batch of B and of A, 64 values per thread) are
+                 * issued BEFORE the wait for the stage: their latency overlaps the wait, and only the
+                 * stores (and, for 64-thread groups, the second A row) follow it. */
                 if (MODE != CV_WGRAD) {
                     /* A: 128 positions x 32 taps; lanes run along the positions (contiguous in the image).
-                     * The 32 loads of a row are issued before its stores. */
+                     * B: filters (fprop) or channels (dgrad) x 32 taps, eight 16-byte chunks per thread and batch. */
                     const int4 *tab4 = (const int4 *)(ktab + k0);               /* two taps per 16-byte read */
-                    #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int ra = gt + h * gthreads;
-                        if (ra >= CV_BM) break;
-                        float v[32];
+                    auto load_a = [&](int h, float (&v)[32]) {
                         #pragma unroll
                         for (int q = 0; q < 16; q++) {
                             const int4 t2 = tab4[q];
                             v[2 * q] = cv_elem(arow[h], make_int2(t2.x, t2.y));
                             v[2 * q + 1] = cv_elem(arow[h], make_int2(t2.z, t2.w));
                         }
+                    };
+                    auto put_a = [&](int h, const float (&v)[32]) {
+                        const int ra = gt + h * gthreads;
                         #pragma unroll
                         for (int q = 0; q < 8; q++)
                             cv_put(a_hi, lo_a, cv_swz((uint32_t)ra * 128u + (uint32_t)q * 16u),
                                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
-                    }
-                    /* B: filters (fprop) or channels (dgrad) x 32 taps, eight chunks' loads in flight at a time */
-                    for (int t0 = gt; t0 < p.bn * 8; t0 += 8 * gthreads) {
-                        float4 v[8];
+                    };
+                    auto load_b = [&](int t0, float4 (&v)[8]) {
                         #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int t = t0 + j * gthreads, r = t >> 3, q = t & 7;
@@ -280,11 +295,30 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                             }
                             v[j] = make_float4(e4[0], e4[1], e4[2], e4[3]);
                         }
+                    };
+                    auto put_b = [&](int t0, const float4 (&v)[8]) {
                         #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int t = t0 + j * gthreads;
                             if (t < p.bn * 8) cv_put(b_hi, lo_b, cv_swz((uint32_t)(t >> 3) * 128u + (uint32_t)(t & 7) * 16u), v[j]);
                         }
+                    };
+                    float4 vb[8];
+                    float va[32];
+                    load_b(gt, vb);
+                    load_a(0, va);
+                    if (!cv_wait_idle_warp(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 0x13)) { ok = false; break; }
+                    CV_STAMP(0, tstamp);
+                    put_b(gt, vb);
+                    put_a(0, va);
+                    if (gthreads < CV_BM) {                                    /* 64-thread groups: rows gt + 64 */
+                        load_a(1, va);
+                        put_a(1, va);
+                    }
+                    CV_STAMP(1, tstamp);
+                    for (int t0 = gt + 8 * gthreads; t0 < p.bn * 8; t0 += 8 * gthreads) {
+                        load_b(t0, vb);
+                        put_b(t0, vb);
                     }
                 } else {
                     /* wgrad.  A: 128 taps x 32 positions; B: filters x 32 positions; lanes run along the
@@ -305,17 +339,8 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                     }
                     const int valid_rows = (int)(p.rows_a - m0 < CV_BM ? p.rows_a - m0 : CV_BM);
                     const int rstep = gthreads / 8;
-                    /* tile rows beyond the last tap stay zero for the whole item: they are cleared once, the
-                     * first time this group fills its stage for the item (3 -> 32 filters have 27 taps: 101
-                     * of the 128 rows would otherwise be stored, hi and lo, in every K block) */
-                    if (zeroed_for != it) {
-                        for (int r = valid_rows + (gt >> 3); r < CV_BM; r += rstep)
-                            cv_put(a_hi, lo_a, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), make_float4(0.0f, 0.0f, 0.0f, 0.0f));
-                        zeroed_for = it;
-                    }
-                    /* eight rows' loads (32 per thread) in flight at a time */
-                    for (int r0 = gt >> 3; r0 < valid_rows; r0 += 8 * rstep) {
-                        float4 v[8];
+                    /* eight rows' loads (32 per thread) per batch */
+                    auto load_a = [&](int r0, float4 (&v)[8]) {
                         #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int r = r0 + j * rstep;
@@ -325,14 +350,8 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                                 v[j] = make_float4(cv_elem(prow[0], tap), cv_elem(prow[1], tap), cv_elem(prow[2], tap), cv_elem(prow[3], tap));
                             }
                         }
-                        #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const int r = r0 + j * rstep;
-                            if (r < valid_rows) cv_put(a_hi, lo_a, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), v[j]);
-                        }
-                    }
-                    for (int r0 = gt >> 3; r0 < p.bn; r0 += 8 * rstep) {
-                        float4 v[8];
+                    };
+                    auto load_b = [&](int r0, float4 (&v)[8]) {
                         #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int r = r0 + j * rstep;
@@ -344,33 +363,77 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                             }
                             v[j] = make_float4(e4[0], e4[1], e4[2], e4[3]);
                         }
+                    };
+                    auto put = [&](uint8_t *hi, uint32_t lo_delta, int r0, int limit, const float4 (&v)[8]) {
                         #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int r = r0 + j * rstep;
-                            if (r < p.bn) cv_put(b_hi, lo_b, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), v[j]);
+                            if (r < limit) cv_put(hi, lo_delta, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), v[j]);
                         }
+                    };
+                    float4 va[8], vb[8];
+                    load_b(gt >> 3, vb);
+                    load_a(gt >> 3, va);
+                    if (!cv_wait_idle_warp(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 0x13)) { ok = false; break; }
+                    CV_STAMP(0, tstamp);
+                    /* tile rows beyond the last tap stay zero for the whole item: they are cleared once, the
+                     * first time this group fills its stage for the item (3 -> 32 filters have 27 taps: 101
+                     * of the 128 rows would otherwise be stored, hi and lo, in every K block) */
+                    if (zeroed_for != it) {
+                        for (int r = valid_rows + (gt >> 3); r < CV_BM; r += rstep)
+                            cv_put(a_hi, lo_a, cv_swz((uint32_t)r * 128u + (uint32_t)q * 16u), make_float4(0.0f, 0.0f, 0.0f, 0.0f));
+                        zeroed_for = it;
+                    }
+                    put(b_hi, lo_b, gt >> 3, p.bn, vb);
+                    put(a_hi, lo_a, gt >> 3, valid_rows, va);
+                    CV_STAMP(1, tstamp);
+                    for (int r0 = (gt >> 3) + 8 * rstep; r0 < valid_rows; r0 += 8 * rstep) {
+                        load_a(r0, va);
+                        put(a_hi, lo_a, r0, valid_rows, va);
+                    }
+                    for (int r0 = (gt >> 3) + 8 * rstep; r0 < p.bn; r0 += 8 * rstep) {
+                        load_b(r0, vb);
+                        put(b_hi, lo_b, r0, p.bn, vb);
                     }
                 }
+                CV_STAMP(2, tstamp);
                 /* generic-proxy writes -> visible to the tensor core's reads; one arrival per warp */
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                CV_STAMP(3, tstamp);
+#ifdef TT_TUNING
+                if (blockIdx.x == 0 && gt == 0 && grp == 0) atomicAdd(&g_cv_dbg[4], 1ull);
+#endif
             }
         }
     } else if (warp == CV_EPI_WARPS) {
-        /* ---------------- MMA issuer ---------------- */
+        /* ---------------- MMA issuer ----------------
+         * One lane runs the loop (measured faster than the whole warp running it with one lane issuing).
+         * A K block's 12 instructions take about 1300 cycles to issue whatever the tile's width: the
+         * floor under this kernel once the producers keep up. */
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool ok = true;
+#ifdef TT_TUNING
+            long long ms = clock64(); const long long kstart = ms;
+#define MM_STAMP(i) do { if (blockIdx.x == 0) { long long n_ = clock64(); atomicAdd(&g_cv_dbg[i], (unsigned long long)(n_ - ms)); ms = n_; } } while (0)
+#else
+#define MM_STAMP(i) do { } while (0)
+#endif
             for (int it = blockIdx.x; it < p.items && ok; it += gridDim.x) {
                 long m0; int kb0, kb1, slice;
                 decode(it, m0, kb0, kb1, slice);
+                MM_STAMP(6);
                 if (!cv_wait_idle(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 0x14)) { ok = false; break; }
+                MM_STAMP(7);
                 tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(acc * bn32);
                 for (int kb = kb0; kb < kb1; kb++) {
+                    MM_STAMP(6);
                     if (!cv_wait_idle(bar_full + 8 * s, ph, abort_flag, p.status, 0x12)) { ok = false; break; }
+                    MM_STAMP(5);
                     tc_fence_after();
                     const uint32_t a_hi = smem_base + (uint32_t)s * stage_bytes;
                     const uint32_t a_lo = a_hi + CV_A_BYTES;
@@ -392,6 +455,9 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                 tc_commit(bar_tfull + 8 * acc);
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
+#ifdef TT_TUNING
+            if (blockIdx.x == 0) { MM_STAMP(6); atomicAdd(&g_cv_dbg[9], (unsigned long long)(clock64() - kstart)); }
+#endif
         }
     } else {
         /* ---------------- epilogue warps: tensor-memory lane quarter `warp` ---------------- */
