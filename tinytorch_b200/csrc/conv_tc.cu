@@ -168,12 +168,15 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
     const uint32_t bar_tempty = bar_tfull + 16;                         /* 2 */
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * p.stages + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
+    float *sbias = (float *)(tmem_slot + 4);                            /* 256: the epilogue reads the bias from here, so its loads
+                                                                          * need not be ordered against the stores of the tile */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bn32 = (p.bn + 31) & ~31;                                 /* accumulator pitch in tensor-memory columns */
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(CV_BM >> 4) << 24);
     const long sp_out = (long)p.Ho * p.Wo, sp_in = (long)p.H * p.W;
 
+    for (int c = threadIdx.x; c < 256; c += CV_THREADS) sbias[c] = (p.bias && c < p.rows_b) ? p.bias[c] : 0.0f;
     for (int k = threadIdx.x; k < ((p.taps + 31) & ~31); k += CV_THREADS) {
         const int hw = p.HH * p.WW, ch = k / hw, rem = k - ch * hw, kh = rem / p.WW, kw = rem - kh * p.WW;
         if (k >= p.taps) { ktab[k] = make_int2(0, 31); wtab[k] = 0; continue; }
@@ -499,7 +502,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1) conv_tc_kernel(ConvParams p) {
                         const int c = c0 + j;
                         if (c < p.rows_b) {
                             float v = __uint_as_float(r[j]);
-                            if (p.bias) v += p.bias[c];
+                            if (p.bias) v += sbias[c];
                             float *o = dst + (long)c * col_stride;
                             *o = p.accumulate ? *o + v : v;
                         }
@@ -584,7 +587,7 @@ static int cv_launch(ConvParams &p) {
     if (stages < 2) { tt_set_error("tcgen05 convolution: tile does not fit shared memory"); return -1; }
     p.stages = stages;
     p.status = g_cv_status_dev;
-    const size_t smem = (size_t)stages * stage + CV_MAX_TAPS * (sizeof(int2) + sizeof(int)) + 8 * (2 * stages + 4) + 16 + 1024;
+    const size_t smem = (size_t)stages * stage + CV_MAX_TAPS * (sizeof(int2) + sizeof(int)) + 8 * (2 * stages + 4) + 16 + 256 * sizeof(float) + 1024;
     static size_t configured[3] = {0, 0, 0};
     void (*kern)(ConvParams) = p.mode == CV_FPROP ? conv_tc_kernel<CV_FPROP> : p.mode == CV_DGRAD ? conv_tc_kernel<CV_DGRAD> : conv_tc_kernel<CV_WGRAD>;
     if (smem > configured[p.mode]) {
