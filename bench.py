@@ -264,7 +264,7 @@ def gemm_block(ns, peaks, cases=((1024, 5), (4096, 5))):
 MLP_GEMM_TRAFFIC = {1: 648.1e6}
 MLP_GEMM_TRAFFIC_SOURCE = "profiles/mlp_step_gemm_dram_traffic.md (ncu, the 11 GEMM launches of one step; 331 MB algorithmic per launch)"
 # sm__pipe_tensor_cycles_active of the pair kernel, from the ncu capture named here (not an estimate)
-TENSOR_PIPE_NCU = {"value": 0.654, "case": "4096^3 forward + backward, gemm_tc2_kernel, sm__pipe_tensor_cycles_active % of elapsed (63.7 / 65.9 / 66.7)",
+TENSOR_PIPE_NCU = {"value": 0.713, "case": "4096^3 forward + backward, gemm_tc2_kernel, sm__pipe_tensor_cycles_active % of elapsed (70.3 / 71.5 / 72.0)",
                    "source": "profiles/gemm_tc2_kernel_square4096.md"}
 
 

@@ -44,6 +44,13 @@
 #define TC_THREADS 448
 #define TC_SPLIT_THREADS 256
 #define TC_EPI_THREADS 128
+#define TC2_THREADS (TC_THREADS + 64)   /* pair kernel: two more warps, which pass this CTA's "tiles landed" and "lo tiles written" on to the leader */
+#ifndef TC2_STAGES
+#define TC2_STAGES 4        /* pair kernel: ring of raw (hi) tiles, 32 KB per stage and CTA */
+#endif
+#ifndef TC2_LO_SLOTS
+#define TC2_LO_SLOTS 3      /* pair kernel: slots for the lo tiles, which live only from the split pass to the cross-term MMAs */
+#endif
 
 #include "tcgen05_utils.cuh"
 
@@ -556,15 +563,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
  * 96 KB and TMA writes 48 KB -- more than one SM's shared memory delivers in the 1536 cycles
  * the MMAs take.  In a pair each CTA stages its own 128 rows of A and HALF of B (128 of the
  * 256 columns); the pair's tensor cores share the B halves, so per SM the MMAs read 96 KB,
- * the split pass moves 64 KB and TMA writes 32 KB, and a stage is 64 KB, which makes room
- * for three.  Loads carry no multicast: each CTA fetches its own tiles.
+ * the split pass moves 64 KB and TMA writes 32 KB.  Loads carry no multicast: each CTA
+ * fetches its own tiles.
+ *
+ * Shared memory holds two rings per CTA: TC2_STAGES stages of raw tiles (A rows + B half,
+ * 32 KB), which TMA fills far ahead, and TC2_LO_SLOTS slots of lo tiles (32 KB), which live only
+ * from the split pass to the cross-term MMAs.  hi*hi needs the raw tiles only and is issued as
+ * soon as both CTAs' loads have landed; lo*hi and hi*lo follow when the slot is written.
  *
  * Protocol (rank 0 of the cluster is the leader and issues every MMA):
- *   full[s]    local : each CTA's TMA bytes for stage s (own A rows, own B half)
- *   lo[s]      leader: 2 x 8 arrivals, one per split warp of BOTH CTAs (remote arrive)
- *   empty[s]   both  : tcgen05.commit multicast from the leader when the MMAs have read stage s
- *   tfull[a]   both  : tcgen05.commit multicast when accumulator a is complete
- *   tempty[a]  leader: 2 x 4 arrivals, one per epilogue warp of both CTAs
+ *   full[s]     local : each CTA's TMA bytes for stage s (own A rows, own B half)
+ *   hi[s]       leader: 2 arrivals, one per CTA, from its "landed" relay thread
+ *   pass[l]     local : 8 arrivals, one per split warp: lo slot l is written
+ *   lo[l]       leader: 2 arrivals, one per CTA, from its "written" relay thread
+ *   empty[s]    both  : tcgen05.commit multicast when the MMAs have read stage s
+ *   loempty[l]  both  : tcgen05.commit multicast when the cross-term MMAs have read slot l
+ *   tfull[a]    both  : tcgen05.commit multicast when accumulator a is complete
+ *   tempty[a]   leader: 2 x 4 arrivals, one per epilogue warp of both CTAs
+ * An arrival at the other CTA's barrier carries a cluster-scope release and blocks the arriving
+ * thread for 1000-1500 cycles (measured with clock stamps): done by the split warps themselves
+ * it was what set the kernel's pace, hence the two relay threads (own warps), which turn the
+ * cheap local arrivals into one remote arrival per CTA; the leader's own relays arrive locally.
  * Every CTA runs its own producer, split and epilogue warps on its own half of the tile. */
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -605,6 +624,15 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
         }
     }
 }
+/* The same for a whole warp (see mbar_wait_warp). */
+__device__ __forceinline__ bool mbar_wait_warp_cluster(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                       uint32_t *status, uint32_t code) {
+    bool got = true;
+    if ((threadIdx.x & 31) == 0) got = mbar_wait_cluster(bar, parity, abort_flag, status, code);
+    got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+    if (got) got = mbar_wait_cluster(bar, parity, abort_flag, status, code);     /* immediate: the phase is complete */
+    return __all_sync(0xffffffffu, got);
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -620,16 +648,44 @@ __device__ __forceinline__ void tc2_mma_tf32(uint32_t d_tmem, uint64_t adesc, ui
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+#ifdef TT_TUNING
+__device__ unsigned long long g_tc_dbg[16];
+extern "C" int ttb_debug_gemm_read(unsigned long long out[16]) {
+    cudaStreamSynchronize(g_tt.stream);
+    unsigned long long z[16] = {0};
+    if (cudaMemcpyFromSymbol(out, g_tc_dbg, sizeof z) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(g_tc_dbg, z, sizeof z);
+    return 0;
+}
+/* phase times are summed in registers and written once when the role ends: a global atomic per stamp
+ * would sit in front of every release fence the role executes */
+#define TC_STAMP(i) do { long long n_ = clock64(); dl[(i) & 3] += (unsigned long long)(n_ - tstamp); tstamp = n_; } while (0)
+__device__ long long g_tc_trace[8 * 12];
+extern "C" int ttb_debug_gemm_trace(long long out[96]) {
+    cudaStreamSynchronize(g_tt.stream);
+    return cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 96) == cudaSuccess ? 0 : -1;
+}
+/* absolute clock of event ev for K blocks 40..47 of CTA 0's first item */
+#define TC_TRACE(ev) do { if (blockIdx.x == 0 && it == pair && kb >= 40 && kb < 48) g_tc_trace[(kb - 40) * 12 + (ev)] = clock64(); } while (0)
+#define TC_STAMP_INIT long long tstamp = clock64(); unsigned long long dl[4] = {0, 0, 0, 0}; (void)tstamp
+#define TC_STAMP_FLUSH(base, n) do { if (blockIdx.x == 0) for (int j_ = 0; j_ < (n); j_++) atomicAdd(&g_tc_dbg[(base) + j_], dl[j_]); } while (0)
+#else
+#define TC_STAMP(i) do { } while (0)
+#define TC_TRACE(ev) do { } while (0)
+#define TC_STAMP_INIT do { } while (0)
+#define TC_STAMP_FLUSH(base, n) do { } while (0)
+#endif
+
 template <int A_MN, int B_MN, int SPLIT_ACC>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
-    constexpr int BK = 32, STAGES = 3;
+    constexpr int BK = 32, STAGES = TC2_STAGES, LO_SLOTS = TC2_LO_SLOTS;
     constexpr int BN = 256, BNH = 128;                       /* pair tile is 256 wide, each CTA stages 128 columns of B */
     constexpr uint32_t A_BYTES = TC_BM * BK * 4;              /* 16 KB: this CTA's 128 rows */
     constexpr uint32_t B_BYTES = BNH * BK * 4;                /* 16 KB: this CTA's half of B */
     constexpr uint32_t BOX = BK * 128;
     constexpr uint32_t HI_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t STAGE_BYTES = 2 * HI_BYTES;
+    constexpr uint32_t LO_BASE = STAGES * HI_BYTES;           /* the lo slots follow the ring of raw tiles */
     /* M = 256 across the pair, N = 256 */
     constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)A_MN << 15) |
                                ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
@@ -640,13 +696,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t *bars = (uint64_t *)(smem_gen + STAGES * STAGE_BYTES);
+    uint64_t *bars = (uint64_t *)(smem_gen + (STAGES + LO_SLOTS) * HI_BYTES);
     const uint32_t bar_full = smem_u32(bars);
-    const uint32_t bar_lo = bar_full + 8 * STAGES;
-    const uint32_t bar_empty = bar_lo + 8 * STAGES;
-    const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+    const uint32_t bar_hi = bar_full + 8 * STAGES;
+    const uint32_t bar_empty = bar_hi + 8 * STAGES;
+    const uint32_t bar_lo = bar_empty + 8 * STAGES;
+    const uint32_t bar_loempty = bar_lo + 8 * LO_SLOTS;
+    const uint32_t bar_pass = bar_loempty + 8 * LO_SLOTS;      /* local: the split warps are done with a slot */
+    const uint32_t bar_tfull = bar_pass + 8 * LO_SLOTS;
     const uint32_t bar_tempty = bar_tfull + 16;
-    uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 4);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 3 * LO_SLOTS + 4);
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -683,8 +742,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_lo + 8 * s, 2 * TC_SPLIT_THREADS / 32);
+            mbar_init(bar_hi + 8 * s, 2);
             mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int l = 0; l < LO_SLOTS; l++) {
+            mbar_init(bar_lo + 8 * l, 2);
+            mbar_init(bar_loempty + 8 * l, 1);
+            mbar_init(bar_pass + 8 * l, TC_SPLIT_THREADS / 32);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(bar_tfull + 8 * a, 1);
@@ -704,6 +768,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     /* the leader's copies of the barriers everybody arrives on */
+    const uint32_t lead_hi = map_to_cta(bar_hi, 0);
     const uint32_t lead_lo = map_to_cta(bar_lo, 0);
     const uint32_t lead_tempty = map_to_cta(bar_tempty, 0);
 
@@ -712,6 +777,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool ok = true;
+            TC_STAMP_INIT;
             auto coords = [&](int m0, int n0, int &ma, int &nb) { ma = m0 + (int)rank * TC_BM; nb = n0 + (int)rank * BNH; };
             auto prefetch = [&](int m0, int n0, int kb) {
                 if (p.noprefetch) return;
@@ -739,8 +805,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         decode(it + num_pairs, m2, n2, kb2, kb3, s2);
                         if (kb2 + (pk - kb1) < kb3) prefetch(m2, n2, kb2 + (pk - kb1));
                     }
+                    TC_STAMP(0);
                     if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
-                    const uint32_t st = smem_base + s * STAGE_BYTES;
+                    TC_STAMP(1);
+                    TC_TRACE(0);
+                    const uint32_t st = smem_base + s * HI_BYTES;
                     const uint32_t full = bar_full + 8 * s;
                     const int k0 = kb * BK;
                     mbar_expect_tx(full, HI_BYTES);
@@ -753,18 +822,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
+            TC_STAMP_FLUSH(0, 2);
             if (!ok) { long long t0 = clock64(); while (clock64() - t0 < 200000) { } }
         }
     } else if (warp == 1) {
         /* ---------------- MMA issuer: the leader CTA only ---------------- */
         if (lane == 0 && rank == 0) {
             int s = 0; uint32_t ph = 0;
+            int l = 0; uint32_t lph = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool ok = true;
+            TC_STAMP_INIT;
+#ifdef TT_TUNING
+            unsigned long long kcount = 0;
+#endif
             for (int it = pair; it < num_items && ok; it += num_pairs) {
                 int m0, n0, kb0, kb1, split;
                 decode(it, m0, n0, kb0, kb1, split);
+                TC_STAMP(0);
                 if (!mbar_wait_cluster(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 4)) { ok = false; break; }
+                TC_STAMP(3);
                 tc_fence_after();
                 uint32_t d_main = tmem_base + (uint32_t)(SPLIT_ACC ? 0 : acc * BN);
                 uint32_t d_corr = SPLIT_ACC ? tmem_base + (uint32_t)BN : d_main;
@@ -772,66 +849,149 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (kb > kb0 && (kb - kb0) % p.chunk_kb == 0) {
                         tc2_commit_both(bar_tfull + 8 * acc);
                         if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+                        TC_STAMP(0);
                         if (!mbar_wait_cluster(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 4)) { ok = false; break; }
+                        TC_STAMP(3);
                         tc_fence_after();
                         d_main = tmem_base + (uint32_t)(SPLIT_ACC ? 0 : acc * BN);
                         d_corr = SPLIT_ACC ? tmem_base + (uint32_t)BN : d_main;
                     }
-                    if (!mbar_wait_cluster(bar_lo + 8 * s, ph, abort_flag, p.status, 2)) { ok = false; break; }
+                    /* the raw tiles are enough for hi*hi: those four MMAs are issued as soon as both CTAs'
+                     * loads have landed, while the split warps still produce the lo tiles */
+                    TC_STAMP(0);
+                    if (!mbar_wait_cluster(bar_hi + 8 * s, ph, abort_flag, p.status, 6)) { ok = false; break; }
+                    TC_STAMP(1);
+                    TC_TRACE(2);
                     tc_fence_after();
-                    const uint32_t a_hi = smem_base + s * STAGE_BYTES;
+                    const uint32_t a_hi = smem_base + s * HI_BYTES;
                     const uint32_t b_hi = a_hi + A_BYTES;
-                    const uint32_t a_lo = a_hi + HI_BYTES;
-                    const uint32_t b_lo = b_hi + HI_BYTES;
-                    #pragma unroll
-                    for (int ks = 0; ks < BK / 8; ks++) {
-                        const uint32_t a_off = A_MN ? ks * 1024 : ks * 32;
-                        const uint32_t b_off = B_MN ? ks * 1024 : ks * 32;
-                        const uint64_t da_hi = make_desc<A_MN, BK>(a_hi + a_off);
-                        const uint64_t db_hi = make_desc<B_MN, BK>(b_hi + b_off);
-                        const uint32_t first = ((kb - kb0) % p.chunk_kb != 0 || ks > 0) ? 1u : 0u;      /* main: restarts with every chunk */
-                        const uint32_t first_corr = SPLIT_ACC ? ((kb > kb0 || ks > 0) ? 1u : 0u) : first;   /* cross terms: run over the whole item */
-                        if (TC_FULL_SPLIT(p)) {
+                    const uint32_t a_lo = smem_base + LO_BASE + l * HI_BYTES;
+                    const uint32_t b_lo = a_lo + A_BYTES;
+                    const bool cross = TC_FULL_SPLIT(p);
+                    if (SPLIT_ACC || !cross) {
+                        #pragma unroll
+                        for (int ks = 0; ks < BK / 8; ks++) {
+                            const uint32_t first = ((kb - kb0) % p.chunk_kb != 0 || ks > 0) ? 1u : 0u;      /* main: restarts with every chunk */
+                            tc2_mma_tf32(d_main, make_desc<A_MN, BK>(a_hi + (A_MN ? ks * 1024 : ks * 32)),
+                                         make_desc<B_MN, BK>(b_hi + (B_MN ? ks * 1024 : ks * 32)), IDESC, first);
+                        }
+                    }
+                    TC_STAMP(0);
+                    TC_TRACE(3);
+                    if (!mbar_wait_cluster(bar_lo + 8 * l, lph, abort_flag, p.status, 2)) { ok = false; break; }
+                    TC_STAMP(2);
+                    TC_TRACE(4);
+#ifdef TT_TUNING
+                    kcount++;
+#endif
+                    tc_fence_after();
+                    if (cross) {
+                        #pragma unroll
+                        for (int ks = 0; ks < BK / 8; ks++) {
+                            const uint32_t a_off = A_MN ? ks * 1024 : ks * 32;
+                            const uint32_t b_off = B_MN ? ks * 1024 : ks * 32;
+                            const uint64_t da_hi = make_desc<A_MN, BK>(a_hi + a_off);
+                            const uint64_t db_hi = make_desc<B_MN, BK>(b_hi + b_off);
                             const uint64_t da_lo = make_desc<A_MN, BK>(a_lo + a_off);
                             const uint64_t db_lo = make_desc<B_MN, BK>(b_lo + b_off);
+                            /* cross terms: with their own accumulator they run over the whole item */
+                            const uint32_t first_corr = (kb > kb0 || ks > 0) ? 1u : 0u;
                             tc2_mma_tf32(d_corr, da_lo, db_hi, IDESC, first_corr);
                             tc2_mma_tf32(d_corr, da_hi, db_lo, IDESC, 1u);
-                            tc2_mma_tf32(d_main, da_hi, db_hi, IDESC, SPLIT_ACC ? first : 1u);
-                        } else {
-                            tc2_mma_tf32(d_main, da_hi, db_hi, IDESC, first);
+                            if (!SPLIT_ACC) tc2_mma_tf32(d_main, da_hi, db_hi, IDESC, 1u);
                         }
                     }
                     tc2_commit_both(bar_empty + 8 * s);
+                    tc2_commit_both(bar_loempty + 8 * l);
+                    TC_TRACE(5);
                     if (++s == STAGES) { s = 0; ph ^= 1; }
+                    if (++l == LO_SLOTS) { l = 0; lph ^= 1; }
                 }
                 if (!ok) break;
                 tc2_commit_both(bar_tfull + 8 * acc);
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
             }
+            TC_STAMP_FLUSH(4, 4);
+#ifdef TT_TUNING
+            if (blockIdx.x == 0) atomicAdd(&g_tc_dbg[12], kcount);
+#endif
         }
     } else if (warp < 2 + TC_SPLIT_THREADS / 32) {
         /* ---------------- split warps: own tiles, report to the leader ---------------- */
         const int st_tid = threadIdx.x - 64;
         int s = 0; uint32_t ph = 0;
+        int l = 0; uint32_t lph = 0;
         bool ok = true;
+        TC_STAMP_INIT;
+#ifdef TT_TUNING
+#define SP_STAMP(i) do { if (st_tid == 0) TC_STAMP(i); } while (0)
+#else
+#define SP_STAMP(i) do { } while (0)
+#endif
         for (int it = pair; it < num_items && ok; it += num_pairs) {
             int m0, n0, kb0, kb1, split;
             decode(it, m0, n0, kb0, kb1, split);
             for (int kb = kb0; kb < kb1; kb++) {
+                SP_STAMP(0);
                 if (!mbar_wait_warp(bar_full + 8 * s, ph, abort_flag, p.status, 1)) { ok = false; break; }
+                SP_STAMP(1);
+                if (st_tid == 0) TC_TRACE(6);
+                /* the lo slot is free once the cross terms of two K blocks ago have been read */
+                if (!mbar_wait_warp_cluster(bar_loempty + 8 * l, lph ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
+                SP_STAMP(2);
+                if (st_tid == 0) TC_TRACE(7);
                 if (TC_MAKE_LO(p)) {
-                    const uint8_t *hi = smem_gen + s * STAGE_BYTES;
+                    const uint8_t *hi = smem_gen + s * HI_BYTES;
+                    uint8_t *lo = smem_gen + LO_BASE + l * HI_BYTES;
                     #pragma unroll 4
                     for (uint32_t c = st_tid; c < HI_BYTES / 16; c += TC_SPLIT_THREADS) {
                         float4 v = *(const float4 *)(hi + c * 16);
                         float4 w = make_float4(split_lo(v.x), split_lo(v.y), split_lo(v.z), split_lo(v.w));
-                        *(float4 *)(hi + HI_BYTES + c * 16) = w;
+                        *(float4 *)(lo + c * 16) = w;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
+                SP_STAMP(3);
+                if (st_tid == 0) TC_TRACE(8);
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(lead_lo + 8 * s);
+                if (lane == 0) mbar_arrive(bar_pass + 8 * l);      /* local and cheap; the relay warp tells the leader */
                 if (++s == STAGES) { s = 0; ph ^= 1; }
+                if (++l == LO_SLOTS) { l = 0; lph ^= 1; }
+            }
+        }
+        if (st_tid == 0) TC_STAMP_FLUSH(8, 4);
+    } else if (warp == TC_THREADS / 32) {
+        /* ---------------- relay: split warps done with a lo slot -> one arrival at the leader ----------------
+         * The arrival at another CTA's barrier carries a cluster-scope release, which costs the arriving
+         * thread about a thousand cycles; here it costs the split warps nothing. */
+        if (lane == 0) {
+            int l = 0; uint32_t lph = 0;
+            bool ok = true;
+            for (int it = pair; it < num_items && ok; it += num_pairs) {
+                int m0, n0, kb0, kb1, split;
+                decode(it, m0, n0, kb0, kb1, split);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(bar_pass + 8 * l, lph, abort_flag, p.status, 8)) { ok = false; break; }
+                    TC_TRACE(9);
+                    if (rank == 0) mbar_arrive(bar_lo + 8 * l); else mbar_arrive_cluster(lead_lo + 8 * l);
+                    TC_TRACE(10);
+                    if (++l == LO_SLOTS) { l = 0; lph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == TC_THREADS / 32 + 1) {
+        /* ---------------- relay: this CTA's raw tiles have landed -> one arrival at the leader ---------------- */
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            bool ok = true;
+            for (int it = pair; it < num_items && ok; it += num_pairs) {
+                int m0, n0, kb0, kb1, split;
+                decode(it, m0, n0, kb0, kb1, split);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 9)) { ok = false; break; }
+                    if (rank == 0) mbar_arrive(bar_hi + 8 * s); else mbar_arrive_cluster(lead_hi + 8 * s);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
             }
         }
     } else {
@@ -1216,7 +1376,7 @@ static int launch_tc(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap
 
 template <int A_MN, int B_MN, int SPLIT_ACC>
 static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUtensorMap &mb, int a_3d, int b_3d) {
-    constexpr size_t smem = (size_t)3 * 2 * (TC_BM * 32 * 4 + 128 * 32 * 4) + 1024 + 8 * (3 * 3 + 4) + 16;
+    constexpr size_t smem = (size_t)(TC2_STAGES + TC2_LO_SLOTS) * (TC_BM * 32 * 4 + 128 * 32 * 4) + 1024 + 8 * (3 * TC2_STAGES + 3 * TC2_LO_SLOTS + 4) + 16;
     static bool configured = false;
     auto kern = gemm_tc2_kernel<A_MN, B_MN, SPLIT_ACC>;
     if (!configured) {
@@ -1243,7 +1403,7 @@ static int launch_tc2_inst(const GemmArgs *g, const CUtensorMap &ma, const CUten
     long pairs = g_plan.units > 0 ? g_plan.units : g_tt.gemm_sms / 2;
     if (items < pairs) pairs = items;
     tt_trace_begin(TTB_K_GEMM_TC);
-    kern<<<(int)(2 * pairs), TC_THREADS, smem, g_tt.stream>>>(ma, mb, p);
+    kern<<<(int)(2 * pairs), TC2_THREADS, smem, g_tt.stream>>>(ma, mb, p);
     g_tt.launches++;
     if (p.tail_tiles) {
         long total4 = (long)p.tail_tiles * 256 * 256 / 4;

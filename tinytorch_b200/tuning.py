@@ -1,12 +1,16 @@
 """Timing aids that exist only in a library built with `make lib EXTRA=-DTT_TUNING`.
 
     python -m tinytorch_b200.tuning conv-phases
+    python -m tinytorch_b200.tuning gemm-phases [N]
 
-prints, for the two convolutions of the CNN workload (batch 256), the clock-cycle stamps the
+The first prints, for the two convolutions of the CNN workload (batch 256), the clock-cycle stamps the
 implicit-GEMM kernel collects in CTA 0: per K block filled by the first producer group the wait for
 the stage, the A tile, the B tile and fence + arrive; for the thread that issues the MMAs the total
-wait for full stages, issue time, wait for a drained accumulator and kernel time.  The production
-library does not export the symbol: the module says so and stops.
+wait for full stages, issue time, wait for a drained accumulator and kernel time.  The second runs
+an N x N x N product (default 4096) on the CTA-pair GEMM kernel and prints CTA 0's cycles per K block
+by role (load thread, MMA thread, first split thread) and the absolute clock of each hand-over for
+eight consecutive K blocks.  The production library does not export the symbols: the module says so
+and stops.
 """
 import ctypes
 import sys
@@ -53,7 +57,54 @@ def conv_phases():
             out.release(); xn.zero_grad(); wn.zero_grad(); bn.zero_grad()
 
 
+def gemm_phases(n=4096):
+    import tinytorch_b200
+    tt = tinytorch_b200.default()
+    try:
+        read, trace = tt.LIB.ttb_debug_gemm_read, tt.LIB.ttb_debug_gemm_trace
+    except AttributeError:
+        raise SystemExit("this library was built without -DTT_TUNING: no phase stamps (make lib EXTRA=-DTT_TUNING)")
+    read.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
+    trace.argtypes = [ctypes.POINTER(ctypes.c_longlong)]
+
+    def stamps():
+        buf = (ctypes.c_ulonglong * 16)()
+        if read(buf) != 0:
+            raise RuntimeError("ttb_debug_gemm_read failed")
+        return list(buf)
+
+    rng = np.random.default_rng(0)
+    a = tt.Node.leaf(rng.standard_normal((n, n)).astype(np.float32), False)
+    b = tt.Node.leaf(rng.standard_normal((n, n)).astype(np.float32), False)
+    for _ in range(3):
+        stamps()
+        c = a.matmul(b)
+        c.value_tensor().to_np()                              # a deferred product runs when its value is read
+        tt.sync()
+        d = stamps()
+        c.release()
+        k = max(d[12], 1)
+        print("K blocks %d | per block: load thread other %.0f wait_empty %.0f | MMA thread issue %.0f wait_raw %.0f "
+              "wait_lo %.0f wait_drained %.0f | split thread wait_raw %.0f wait_slot %.0f pass %.0f arrive %.0f"
+              % (k, d[0] / k, d[1] / k, d[4] / k, d[5] / k, d[6] / k, d[7] / k, d[9] / k, d[10] / k, d[11] / k, d[8] / k))
+    buf = (ctypes.c_longlong * 96)()
+    trace(buf)
+    t = list(buf)
+    names = {0: "load:stage free", 2: "mma:raw tiles seen", 3: "mma:hi*hi issued", 4: "mma:lo slot seen",
+             5: "mma:cross terms issued", 6: "split:raw tiles seen", 7: "split:slot free", 8: "split:pass done",
+             9: "relay:pass seen", 10: "relay:arrived at the leader"}
+    seen = [v for v in t if v > 0]
+    if seen:
+        base = min(seen)
+        for kb in range(8):
+            row = t[kb * 12:(kb + 1) * 12]
+            print("K block", 40 + kb, "  ".join("%s=%d" % (names[e], row[e] - base) for e in sorted(names)))
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2 or sys.argv[1] != "conv-phases":
+    if len(sys.argv) >= 2 and sys.argv[1] == "conv-phases":
+        conv_phases()
+    elif len(sys.argv) >= 2 and sys.argv[1] == "gemm-phases":
+        gemm_phases(int(sys.argv[2]) if len(sys.argv) > 2 else 4096)
+    else:
         raise SystemExit(__doc__)
-    conv_phases()
