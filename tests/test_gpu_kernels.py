@@ -386,7 +386,10 @@ def test_sgemm_rowmajor_host_pointers(tt, orc):
 TC_SHAPES = [(128, 128, 128), (128, 256, 64), (256, 256, 256), (1024, 1024, 1024), (384, 512, 1000), (100, 260, 72),
              (129, 36, 260), (640, 4096, 384), (2048, 64, 2048), (300, 8192, 200),
              # more tiles than SMs with a short last wave: only the last wave's tiles are cut along K (ragged edges)
-             (1500, 2048, 3500), (2304, 1024, 2560)]
+             (1500, 2048, 3500), (2304, 1024, 2560),
+             # CTA-pair kernel with reductions shorter than, equal to and just beyond its rings (four raw stages,
+             # three lo slots), and several short items per pair (the rings' phases run on across items)
+             (512, 32, 512), (512, 96, 768), (768, 160, 512), (4096, 96, 2304)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
