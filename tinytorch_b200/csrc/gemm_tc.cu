@@ -649,10 +649,10 @@ __device__ __forceinline__ void tc2_mma_tf32(uint32_t d_tmem, uint64_t adesc, ui
 }
 
 #ifdef TT_TUNING
-__device__ unsigned long long g_tc_dbg[16];
-extern "C" int ttb_debug_gemm_read(unsigned long long out[16]) {
+__device__ unsigned long long g_tc_dbg[24];
+extern "C" int ttb_debug_gemm_read(unsigned long long out[24]) {
     cudaStreamSynchronize(g_tt.stream);
-    unsigned long long z[16] = {0};
+    unsigned long long z[24] = {0};
     if (cudaMemcpyFromSymbol(out, g_tc_dbg, sizeof z) != cudaSuccess) return -1;
     cudaMemcpyToSymbol(g_tc_dbg, z, sizeof z);
     return 0;
@@ -999,6 +999,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int q = warp & 3;
         int acc = 0; uint32_t acc_ph = 0;
         bool ok = true;
+        TC_STAMP_INIT;
+#ifdef TT_TUNING
+        unsigned long long drains = 0;
+#define EP_STAMP(i) do { if (warp == 10 && lane == 0) TC_STAMP(i); } while (0)
+#else
+#define EP_STAMP(i) do { } while (0)
+#endif
         for (int it = pair; it < num_items && ok; it += num_pairs) {
             int m0, n0, kb0, kb1, split;
             decode(it, m0, n0, kb0, kb1, split);
@@ -1031,7 +1038,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const bool finish_after = e.partial && (e.relu || e.mrow);
                 const int fin_relu = e.relu; const float *fin_mrow = e.mrow;
                 if (finish_after) { e.relu = 0; e.mrow = nullptr; }
+                EP_STAMP(3);
                 if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 5)) { ok = false; break; }
+                EP_STAMP(0);
+#ifdef TT_TUNING
+                drains++;
+#endif
                 tc_fence_after();
                 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -1048,7 +1060,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (c0 + 32 >= BN) {
                         tc_fence_before();
                         __syncwarp();
+                        EP_STAMP(1);
                         if (lane == 0) mbar_arrive_cluster(lead_tempty + 8 * acc);
+                        EP_STAMP(2);
                     }
                     const int gc = n0 + c0;
                     if (row < p.M && gc < p.N) {
@@ -1074,6 +1088,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
             }
         }
+#ifdef TT_TUNING
+        if (warp == 10 && lane == 0) { EP_STAMP(3); TC_STAMP_FLUSH(16, 4); if (blockIdx.x == 0) atomicAdd(&g_tc_dbg[20], drains); }
+#endif
     }
 
     tc_fence_before();

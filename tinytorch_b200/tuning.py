@@ -68,7 +68,7 @@ def gemm_phases(n=4096):
     trace.argtypes = [ctypes.POINTER(ctypes.c_longlong)]
 
     def stamps():
-        buf = (ctypes.c_ulonglong * 16)()
+        buf = (ctypes.c_ulonglong * 24)()
         if read(buf) != 0:
             raise RuntimeError("ttb_debug_gemm_read failed")
         return list(buf)
@@ -87,6 +87,9 @@ def gemm_phases(n=4096):
         print("K blocks %d | per block: load thread other %.0f wait_empty %.0f | MMA thread issue %.0f wait_raw %.0f "
               "wait_lo %.0f wait_drained %.0f | split thread wait_raw %.0f wait_slot %.0f pass %.0f arrive %.0f"
               % (k, d[0] / k, d[1] / k, d[4] / k, d[5] / k, d[6] / k, d[7] / k, d[9] / k, d[10] / k, d[11] / k, d[8] / k))
+        n = max(d[20], 1)
+        print("    epilogue warp, per accumulator hand-over (%d): wait_full %.0f  loads and first stores %.0f  arrive %.0f  "
+              "remaining stores %.0f" % (n, d[16] / n, d[17] / n, d[18] / n, d[19] / n))
     buf = (ctypes.c_longlong * 96)()
     trace(buf)
     t = list(buf)
