@@ -100,7 +100,11 @@ struct TcParams {
     int group_m;             /* tile rows per rasterisation group (tc_tile_coords) */
     int push_on;             /* send the parts of C other ranks own into their staging areas (PeerPush) */
     PeerPush push;
-    uint32_t *status;        /* host-mapped: 0 = fine, else wait code | cta << 8 */
+    /* host-mapped: 0 = fine, else wait code | cta << 8.  Codes name the wait that gave up: 1 split warps on a
+     * stage's loads, 2 MMA thread on a lo tile, 3 load thread on a free stage, 4 MMA thread on a drained
+     * accumulator, 5 epilogue on a full accumulator; pair kernel also 6 MMA thread on both CTAs' raw tiles,
+     * 7 split warps on a free lo slot, 8 / 9 the relay threads on the split warps / on the loads. */
+    uint32_t *status;
 };
 
 /* Tile number -> tile coordinates.  Tiles are numbered so that the CTAs that run at the same time
