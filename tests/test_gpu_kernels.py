@@ -415,6 +415,28 @@ def test_tensor_core_gemm_all_three_products(tt, shape):
     assert max(errs.values()) <= TC_TOL, errs
 
 
+def test_tensor_core_gemm_random_shapes(tt):
+    """Forty seeded random shapes on the CTA-pair kernel (M >= 256, 256-wide tiles): every count of K blocks
+    from 1 to 40 occurs against rings of four and three slots, with ragged M and N edges; same tolerance."""
+    rng = np.random.default_rng(2024)
+    tt.LIB.ttb_set_gemm_path(1)
+    worst = {}
+    try:
+        for kblocks in range(1, 41):
+            m = int(rng.integers(256, 900))
+            n = 4 * int(rng.integers(64, 300))                   # rows of C and B stay 16-byte multiples
+            k = 32 * kblocks - 4 * int(rng.integers(0, 8))       # the last K block may be partial
+            a = rng.standard_normal((m, k)).astype(np.float32)
+            b = rng.standard_normal((k, n)).astype(np.float32)
+            err = rel_err(run2(tt, "tt_matmul_fast", a, b), a.astype(np.float64) @ b.astype(np.float64))
+            if err > TC_TOL:
+                worst[(m, k, n)] = err
+    finally:
+        tt.LIB.ttb_set_gemm_path(0)
+    tt.sync()
+    assert not worst, worst
+
+
 def test_tensor_core_gemm_is_no_worse_than_the_reference_arithmetic(tt, orc):
     """Against float64 the 3xTF32 product must be about as accurate as the
     reference's own fp32 chain on the same inputs."""
