@@ -124,7 +124,8 @@ extern "C" int ttb_dist_init(int rank, int world, const char id_in[128]) {
     if (nccl_bind() != 0) return -1;
     /* From four ranks on the GEMMs leave the SMs their wave count does not need to the collective
      * (gemm_tc.cu, TT_TC_FIT); NCCL is then held to the CTAs that fit there, unless the caller has
-     * set NCCL_MAX_CTAS.  Measured together: 8 GPUs 2.65 -> 2.53 ms per step; either one alone loses. */
+     * set NCCL_MAX_CTAS.  Measured together on an earlier build: 8 GPUs 2.65 -> 2.53 ms per step; either one
+     * alone loses. */
     int fit = 1, from = 4;
 #ifdef TT_TUNING
     {
@@ -136,15 +137,24 @@ extern "C" int ttb_dist_init(int rank, int world, const char id_in[128]) {
     const bool cap = fit && world >= from && !getenv("NCCL_MAX_CTAS");
     ncclUniqueId id;
     memcpy(id.internal, id_in, 128);
-    if (cap && nccl.CommInitRankConfig && nccl.CommSplit && !getenv("TT_DP_TAIL_COMM_OFF")) {
+    /* How many CTAs NCCL gets was measured on the benchmark MLP with 4 and 8 GPUs: ONE communicator with 24 CTAs.
+     * Eight GPUs: 2.49-2.50 ms per step (16 CTAs plus a second communicator for the last reduction of a step:
+     * 2.65; 32 CTAs: 2.50); four GPUs: 3.59 (16 + second communicator 3.65).  What is exposed at the end of the
+     * backward pass shrinks by more (8 GPUs 0.65 -> 0.39 ms) than the GEMMs lose to the eight extra CTAs (1.82
+     * -> 1.96 ms).  The second communicator remains available: TT_DP_TAIL_COMM=1. */
+    const int main_ctas = 24;
+    const bool want_tail = nccl.CommSplit && getenv("TT_DP_TAIL_COMM") && atoi(getenv("TT_DP_TAIL_COMM")) == 1;
+    if (cap && nccl.CommInitRankConfig) {
         /* main communicator capped by its configuration (not by the environment, which would cap the
          * second one too); tail communicator split off it with NCCL's own default */
-        TtNcclConfig main_cfg = nccl_config(16);
+        TtNcclConfig main_cfg = nccl_config(main_ctas);
         if (!nccl_ok(nccl.CommInitRankConfig(&g_comm, world, id, rank, &main_cfg), "ncclCommInitRankConfig")) { g_comm = nullptr; return -1; }
-        TtNcclConfig tail_cfg = nccl_config(TT_NCCL_UNDEF_INT);
-        if (nccl.CommSplit(g_comm, 0, rank, &g_comm_tail, &tail_cfg) != 0) g_comm_tail = nullptr;     /* optional: the main one serves */
+        if (want_tail) {
+            TtNcclConfig tail_cfg = nccl_config(TT_NCCL_UNDEF_INT);
+            if (nccl.CommSplit(g_comm, 0, rank, &g_comm_tail, &tail_cfg) != 0) g_comm_tail = nullptr;     /* optional: the main one serves */
+        }
     } else {
-        if (cap) setenv("NCCL_MAX_CTAS", "16", 0);
+        if (cap) setenv("NCCL_MAX_CTAS", "24", 0);
         if (!nccl_ok(nccl.CommInitRank(&g_comm, world, id, rank), "ncclCommInitRank")) { g_comm = nullptr; return -1; }
     }
     if (!tt_cuda_ok(cudaEventCreateWithFlags(&g_ev_ready, cudaEventDisableTiming), "cudaEventCreate") ||
