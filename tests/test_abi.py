@@ -36,6 +36,19 @@ def test_library_exports_every_declared_symbol(ns):
     assert not missing, missing
 
 
+def test_shipped_library_is_not_a_tuning_build(ns):
+    """The clock-stamp readers and the wrong-numbers-by-design timing modes exist only in a library built
+    with -DTT_TUNING; the one in the tree must not be such a build, and the tuning module must say so
+    instead of printing figures."""
+    for name in ("ttb_debug_gemm_read", "ttb_debug_gemm_trace", "ttb_debug_conv_read"):
+        assert not hasattr(ns.LIB, name), name
+    from tinytorch_b200 import tuning
+    for run in (tuning.gemm_phases, tuning.conv_phases):
+        with pytest.raises(SystemExit) as why:
+            run()
+        assert "TT_TUNING" in str(why.value)
+
+
 def test_reference_abi_is_a_subset(ns):
     """The 43 symbols of the reference library (nm -D of its build) are all here."""
     from tinytorch_b200 import api
