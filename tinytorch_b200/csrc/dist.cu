@@ -68,9 +68,10 @@ static struct {
 } nccl;
 
 static ncclComm_t g_comm = nullptr;
-/* A second communicator over the same ranks for the reductions nothing is left to hide behind (the last
- * row block of the last weight gradient of a pass): the first one is held to the few CTAs that fit beside
- * the GEMMs, this one may take the SMs the finished backward pass has left idle. */
+/* Optional (TT_DP_TAIL_COMM=1): a second communicator over the same ranks for the reductions nothing is left
+ * to hide behind (the last row block of the last weight gradient of a pass).  The first one is held to the
+ * CTAs that fit beside the GEMMs, this one may take the SMs the finished backward pass has left idle.  Without
+ * it those reductions run on the first communicator. */
 static ncclComm_t g_comm_tail = nullptr;
 static int g_world = 1, g_rank = 0;
 static cudaEvent_t g_ev_ready = nullptr, g_ev_done = nullptr;
